@@ -14,8 +14,8 @@ import math
 import torch
 
 
-def embed(table, ids, out):
-    out.copy_(table[ids.long()].float())
+def embed(table, ids, out, scale=1.0):
+    out.copy_(table[ids.long()].float() * float(torch.tensor(scale, dtype=torch.float32)))
 
 
 def add_rmsnorm(h, delta, gain, eps, out, rows=None):
@@ -86,7 +86,8 @@ def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gai
 
 
 def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cache, page_size,
-                      block_tables, seq_ids, positions, scale, window, value_dim=None, sinks=None):
+                      block_tables, seq_ids, positions, scale, window, value_dim=None, sinks=None,
+                      softcap=0.0, value_row=0):
     T = q.shape[0]
     group = num_heads // num_kv_heads
     dv = value_dim or head_dim
@@ -103,9 +104,11 @@ def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cach
         for h in range(num_heads):
             g = h // group
             K = k_cache[pages, g, offs, :].float()
-            V = v_cache[pages, g, offs, :].float()
+            V = v_cache[pages, g, offs, :dv].float()
             qv = q[t, h * head_dim:(h + 1) * head_dim].float()
             s = (K @ qv) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
             if sinks is not None:
                 w = torch.softmax(torch.cat([s, sinks[h:h + 1].float()]), dim=0)[:-1]
             else:
@@ -127,17 +130,19 @@ def linear(x, w, out_dtype=None, residual=None):
     return y.to(out_dtype or x.dtype)
 
 
-def gated_linear(x, w_gate_up, interleaved, activation="silu"):
+def gated_linear(x, w_gate_up, interleaved, activation="silu", bias=None):
     gu = (x.float() @ w_gate_up.float().t()).to(x.dtype)
     out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=x.dtype)
-    if activation == "silu":
+    if activation == "silu" and bias is None:
         swiglu(gu, out, interleaved)
     else:
-        gated_act(gu, out, interleaved, activation)
+        gated_act(gu, out, interleaved, activation, bias)
     return out
 
 
-def gated_act(gate_up, out, interleaved, activation):
+def gated_act(gate_up, out, interleaved, activation, bias=None):
+    if bias is not None:
+        gate_up = gate_up.float() + bias
     g, u = _gate(gate_up, out.shape[1], interleaved)
     if activation == "relu":
         a = torch.relu(g)
@@ -432,11 +437,124 @@ def weighted_sum(parts, scales, out):
         out.add_(p.float() * float(torch.tensor(s, dtype=torch.float32)))
 
 
+def scaled_add_norm(h, y, bias, alpha, gain, eps, act=None):
+    s = float(torch.tensor(alpha, dtype=torch.float32)) * h + y.float()
+    if bias is not None:
+        s = s + bias
+    h.copy_(s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * gain)
+    if act is not None:
+        act.copy_(h.to(act.dtype))
+
+
+def add_bias(y, bias):
+    y.copy_((y.float() + bias).to(y.dtype))
+
+
+def _turn(y, rope, rot, interleaved):
+    """y [T, heads, width] float32: the first `rot` channels rotated by rope [T, rot]."""
+    if rope is None or rot == 0:
+        return y
+    half = rot // 2
+    cos, sin = rope[:, None, :half], rope[:, None, half:]
+    if interleaved:
+        a, b = y[..., 0:rot:2].clone(), y[..., 1:rot:2].clone()
+        y[..., 0:rot:2] = a * cos - b * sin
+        y[..., 1:rot:2] = b * cos + a * sin
+    else:
+        a, b = y[..., :half].clone(), y[..., half:rot].clone()
+        y[..., :half] = a * cos - b * sin
+        y[..., half:rot] = b * cos + a * sin
+    return y
+
+
+def qk_rownorm_rope_cache(q, k, v, num_heads, num_kv_heads, key_dim, value_dim, q_gain, k_gain, eps,
+                          rope, rotary_dim, interleaved, slots, k_cache, v_cache, page_size):
+    T = q.shape[0]
+
+    def treat(x, heads, gain):
+        y = x.float()
+        if gain is not None:
+            y = y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps) * gain
+        return _turn(y.reshape(T, heads, key_dim).clone(), rope, rotary_dim, interleaved)
+
+    q.copy_(treat(q, num_heads, q_gain).reshape(T, -1).to(q.dtype))
+    if k is None:
+        return
+    kk = treat(k, num_kv_heads, k_gain)
+    vv = v.reshape(T, num_kv_heads, value_dim) if v is not None else None
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = s // page_size, s % page_size
+        k_cache[page, :, off, :] = kk[t].to(k_cache.dtype)
+        if vv is not None:
+            v_cache[page, :, off, :] = vv[t]
+
+
+def latent_row_cache(kv, rank, width, gain, eps, rope, rotary_dim, interleaved, slots, cache,
+                     page_size):
+    T = kv.shape[0]
+    c = kv[:, :rank].float()
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * gain
+    r = _turn(kv[:, rank:].float().reshape(T, 1, width).clone(), rope, rotary_dim, interleaved)
+    row = torch.cat([c, r.reshape(T, width)], dim=1).to(cache.dtype)
+    flat = cache.reshape(-1, rank + width)
+    for t in range(T):
+        s = int(slots[t])
+        if s >= 0:
+            flat[s] = row[t]
+
+
+def rope_slice(src, src_head, src_off, dst, dst_head, dst_off, num_heads, width, rope, rotary_dim,
+               interleaved):
+    T = src.shape[0]
+    y = torch.stack([src[:, h * src_head + src_off:h * src_head + src_off + width]
+                     for h in range(num_heads)], dim=1).float()
+    y = _turn(y.clone(), rope, rotary_dim, interleaved)
+    for h in range(num_heads):
+        dst[:, h * dst_head + dst_off:h * dst_head + dst_off + width] = y[:, h].to(dst.dtype)
+
+
+def head_linear(x, x_head, w, y, y_head):
+    H, N, K = w.shape
+    for h in range(H):
+        y[:, h * y_head:h * y_head + N] = \
+            (x[:, h * x_head:h * x_head + K].float() @ w[h].float().t()).to(y.dtype)
+
+
+def mlstm(q, k, v, gate_i, gate_f, bias_i, bias_f, cap, q_scale, out, num_seqs, num_heads, key_dim,
+          value_dim, q_start, state_slots, state):
+    H, dk, dv = num_heads, key_dim, value_dim
+    cap = float(torch.tensor(cap, dtype=torch.float32))
+    q_scale = float(torch.tensor(q_scale, dtype=torch.float32))
+    for b in range(num_seqs):
+        row = state[int(state_slots[b])]
+        S = row[:H * dk * dv].view(H, dk, dv)
+        n = row[H * dk * dv:H * dk * dv + H * dk].view(H, dk)
+        m = row[H * dk * dv + H * dk:H * dk * dv + H * dk + H]
+        for t in range(int(q_start[b]), int(q_start[b + 1])):
+            qt = q[t].float().reshape(H, dk) * q_scale
+            kt = k[t].float().reshape(H, dk)
+            vt = v[t].float().reshape(H, dv)
+            li = cap * torch.tanh((gate_i[t] + bias_i) / cap)
+            lf = torch.nn.functional.logsigmoid(cap * torch.tanh((gate_f[t] + bias_f) / cap))
+            m_new = torch.maximum(lf + m, li)
+            keep, take = torch.exp(lf + m - m_new), torch.exp(li - m_new)
+            S.copy_(keep[:, None, None] * S + take[:, None, None] * kt[:, :, None] * vt[:, None, :])
+            n.copy_(keep[:, None] * n + take[:, None] * kt)
+            m.copy_(m_new)
+            num = torch.einsum("hkv,hk->hv", S, qt)
+            den = torch.maximum((n * qt).sum(-1).abs(), torch.exp(-m_new)) + 1e-6
+            out[t] = (num / den[:, None]).reshape(-1)
+
+
 def attention_sink_supports(num_heads, num_kv_heads, key_dim, value_dim):
     return False
 
 
-NAMES = ["gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
+NAMES = ["scaled_add_norm", "add_bias", "qk_rownorm_rope_cache", "latent_row_cache", "rope_slice",
+         "head_linear", "mlstm", "gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
          "moe_feed_forward", "weighted_sum", "attention_sink_supports", "rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
          "attention_generic", "linear", "gated_linear", "sgemm_tn", "gated_act", "cast_rows",
          "group_norm_scale_add", "group_norm_rows", "softcap", "value_norm_share_cache",

@@ -96,6 +96,19 @@ class MixerSpec:
     # each one's result
     branches: tuple = ()
     branch_scales: tuple = ()
+    # attention kinds: c > 0 bounds every scaled score by c tanh(score / c); None: no bound
+    softcap: Optional[float] = None
+    # where qk_norm takes its mean: "head" (every head's channels alone, a gain of head_dim) or
+    # "row" (all heads of a token at once, a gain as wide as the whole projection)
+    qk_norm_scope: str = "head"
+    # latent attention kinds: width of the latent that keys and values are expanded from and
+    # of the latent the queries go through; width of the rotated key part all heads share
+    # (head_dim then counts the unrotated channels of a head's query and key)
+    latent_rank: int = 0
+    query_rank: int = 0
+    rope_dim: int = 0
+    # gated recurrences: the bound c of a gate's pre-activation, c tanh(x / c)
+    gate_cap: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -113,6 +126,7 @@ class FeedForwardSpec:
     top: int = 0
     router_bias: bool = False
     shared: Optional["FeedForwardSpec"] = None
+    bias: bool = False                   # dense kinds: every projection carries a bias
 
 
 @dataclass(frozen=True)
@@ -127,6 +141,9 @@ class LayerSpec:
     feed_forward: Optional[FeedForwardSpec]      # None: the layer has no feed-forward
     norm: NormSpec
     tensors: tuple = ()
+    # blocks that norm the sum: the factor on the stream in stream <- norm(factor * stream +
+    # sublayer(stream))
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -156,6 +173,7 @@ class ModelSpec:
     tied_head_alias: Optional[str] = None   # name a tied checkpoint may ship anyway
     max_positions: int = 0           # advisory, as in the reference
     logit_softcap: Optional[float] = None   # c: logits <- c tanh(logits / c)
+    embedding_scale: float = 1.0     # the embedding rows are multiplied by this
     source: dict = field(default_factory=dict)   # the config.json it came from
 
     @property

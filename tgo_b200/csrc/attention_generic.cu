@@ -10,18 +10,23 @@
 // Keys are dh wide and values dv wide (two cache planes with rows of their own when they
 // differ). With `sinks` (float32, one number per query head) the softmax's denominator also
 // holds exp(sink_h): a key that is always seen, is not scaled and has no value.
+// `softcap` > 0 bounds every score: s <- softcap * tanh(s / softcap), after the scale.
+// A value row starts `v_row` elements after the one before it: dv for a plane of values; the
+// key rows' width when a value is the first dv channels of its key row (one cache plane that
+// serves as both, v_cache = k_cache).
 #include "common.cuh"
 
-#define AG_MAX_DH 256
+#define AG_MAX_DH 256            // rows up to this wide take the instance with 8 sums a lane
+#define AG_MAX_WIDE 640          // wider ones, up to this, the instance with 20
 #define AG_WARPS 4
 
-template <typename T>
+template <typename T, int NACC>
 __global__ void attention_generic_kernel(
     const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
     int H, int Hkv, int dh, int dv, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     int page_size, const int* __restrict__ block_tables, int max_blocks,
     const int* __restrict__ seq_ids, const int* __restrict__ positions, float scale, int window,
-    const float* __restrict__ sinks) {
+    const float* __restrict__ sinks, float softcap, int v_row) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -38,9 +43,9 @@ __global__ void attention_generic_kernel(
 
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     float m = -INFINITY, l = 0.f;
-    float acc[AG_MAX_DH / 32];
+    float acc[NACC];
 #pragma unroll
-    for (int i = 0; i < AG_MAX_DH / 32; ++i) acc[i] = 0.f;
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
     for (int base = lo; base <= p; base += 32) {
         const int j = base + lane;
@@ -52,20 +57,21 @@ __global__ void attention_generic_kernel(
             float a = 0.f;
             for (int d = 0; d < dh; ++d) a += qs[d] * to_f32(kr[d]);
             s = a * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);          // m = -inf the first time: corr = 0
         const float w = j <= p ? expf(s - m_new) : 0.f;
         l = l * corr + warp_sum(w);
 #pragma unroll
-        for (int i = 0; i < AG_MAX_DH / 32; ++i) acc[i] *= corr;
+        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
         for (int jj = 0; jj < nvalid; ++jj) {
             const float wj = __shfl_sync(0xffffffffu, w, jj);
             const int kj = base + jj;
             const int page = bt[kj / page_size];
-            const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + (kj % page_size)) * dv;
+            const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + (kj % page_size)) * v_row;
 #pragma unroll
-            for (int i = 0; i < AG_MAX_DH / 32; ++i) {
+            for (int i = 0; i < NACC; ++i) {
                 const int d = lane + 32 * i;
                 if (d < dv) acc[i] += wj * to_f32(vr[d]);
             }
@@ -78,12 +84,12 @@ __global__ void attention_generic_kernel(
         const float corr = expf(m - m_new);
         l = l * corr + expf(sk - m_new);
 #pragma unroll
-        for (int i = 0; i < AG_MAX_DH / 32; ++i) acc[i] *= corr;
+        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
     }
     T* o = out + (size_t)t * out_stride + (size_t)h * dv;
     const float inv = l > 0.f ? 1.f / l : 0.f;     // position < 0: no keys, zeros out
 #pragma unroll
-    for (int i = 0; i < AG_MAX_DH / 32; ++i) {
+    for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
         if (d < dv) o[d] = from_f32<T>(acc[i] * inv);
     }
@@ -94,24 +100,26 @@ TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
                                   const void* k_cache, const void* v_cache, int page_size,
                                   const int* block_tables, int max_blocks, const int* seq_ids,
                                   const int* positions, float scale, int window,
-                                  const float* sinks, cudaStream_t stream) {
+                                  const float* sinks, float softcap, int v_row, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (dh <= 0 || dh > AG_MAX_DH || dv <= 0 || dv > AG_MAX_DH || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0 ||
-        max_blocks <= 0 || window < 0)
+    if (v_row <= 0) v_row = dv;
+    if (dh <= 0 || dh > AG_MAX_WIDE || dv <= 0 || dv > AG_MAX_WIDE || H <= 0 || Hkv <= 0 || H % Hkv ||
+        page_size <= 0 || max_blocks <= 0 || window < 0 || v_row < dv || !(softcap >= 0.f))
         return TGO_E_BAD_ARG;
+    const bool wide = dv > AG_MAX_DH;
     const dim3 grid(T, (H + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * dh * sizeof(float);
-    if (dtype == TGO_BF16)
-        attention_generic_kernel<bf16><<<grid, AG_WARPS * 32, smem, stream>>>(
-            (const bf16*)q, q_stride, (bf16*)out, out_stride, H, Hkv, dh, dv, (const bf16*)k_cache,
-            (const bf16*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale,
-            window, sinks);
-    else if (dtype == TGO_F32)
-        attention_generic_kernel<float><<<grid, AG_WARPS * 32, smem, stream>>>(
-            (const float*)q, q_stride, (float*)out, out_stride, H, Hkv, dh, dv, (const float*)k_cache,
-            (const float*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale,
-            window, sinks);
-    else
+#define AG_GO(TT, NACC)                                                                            \
+    attention_generic_kernel<TT, NACC><<<grid, AG_WARPS * 32, smem, stream>>>(                         \
+        (const TT*)q, q_stride, (TT*)out, out_stride, H, Hkv, dh, dv, (const TT*)k_cache,              \
+        (const TT*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale, window,   \
+        sinks, softcap, v_row)
+    if (dtype == TGO_BF16) {
+        if (wide) AG_GO(bf16, AG_MAX_WIDE / 32); else AG_GO(bf16, AG_MAX_DH / 32);
+    } else if (dtype == TGO_F32) {
+        if (wide) AG_GO(float, AG_MAX_WIDE / 32); else AG_GO(float, AG_MAX_DH / 32);
+    } else
         return TGO_E_BAD_ARG;
+#undef AG_GO
     return launch_status();
 }

@@ -5,7 +5,10 @@
 //   w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))
 //   out_i       = sum_j w(i, j) v_j
 //
-// (window 0: every earlier key; sinks null: no sink.) One CTA takes a tile of query rows of
+// (window 0: every earlier key; sinks null: no sink.) With a soft cap c > 0 the scaled score
+// goes through c tanh(score / c) first. A value row lies `v_row` elements after the one before
+// it: dv for a plane of values, the key rows' width when a value is the first dv channels of
+// its key row (one cache plane that serves as both). One CTA takes a tile of query rows of
 // one request and one kv head: the rows are the (token, query head of the group) pairs of up
 // to 128/G consecutive tokens, G = H/Hkv, so every row of the tile reads the same keys and
 // values. Keys [page][kv head][offset][dk] and values [page][kv head][offset][dv] come through
@@ -31,6 +34,12 @@
 #define AS_LOG2E 1.4426950408889634f
 #define AS_PAGES 320             // block-table entries of a CTA's key range kept in shared memory
 
+// A raw product q . k as the softmax's exponent in base 2: scaled, and with a soft cap c
+// (cap_log2 = c log2 e > 0, scale_over_cap = scale / c) bounded by c tanh(scale (q . k) / c).
+__device__ __forceinline__ float as_scored(float qk, float scale_log2, float cap_log2, float scale_over_cap) {
+    return cap_log2 > 0.f ? cap_log2 * tanhf(qk * scale_over_cap) : qk * scale_log2;
+}
+
 template <int DK, int DV>
 __global__ void __launch_bounds__(AS_WARPS * 32)
 attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
@@ -41,7 +50,7 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
                       int Hkv, int dk, int dv, float scale_log2, int window,
                       const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
-                      float* __restrict__ part_ml) {
+                      float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row) {
     constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
     constexpr int KS = DK / 16;
     constexpr int CHK = DK / 8, CHV = DV / 8;  // 16-byte chunks per padded row
@@ -106,7 +115,7 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
             size_t off = 0;
             if (ok) {
                 const int pi = j / page_size, po = j - pi * page_size;
-                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dv + c * 8;
+                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * v_row + c * 8;
             }
             cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
         }
@@ -182,8 +191,8 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
                         const int j = kbase + i * 8 + e;
                         const bool a = full || (j <= pos_row[rw][0] && j >= vis_row[rw][0]);
                         const bool c = full || (j <= pos_row[rw][1] && j >= vis_row[rw][1]);
-                        s[rw][i][e] = a ? s[rw][i][e] * scale_log2 : -INFINITY;
-                        s[rw][i][2 + e] = c ? s[rw][i][2 + e] * scale_log2 : -INFINITY;
+                        s[rw][i][e] = a ? as_scored(s[rw][i][e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                        s[rw][i][2 + e] = c ? as_scored(s[rw][i][2 + e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
                         mx[0] = fmaxf(mx[0], s[rw][i][e]);
                         mx[1] = fmaxf(mx[1], s[rw][i][2 + e]);
                     }
@@ -297,7 +306,7 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                              const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
                              int Hkv, int dk, int dv, float scale_log2, int window,
                              const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
-                             float* __restrict__ part_ml) {
+                             float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row) {
     constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
     constexpr int KS = DK / 16;
     constexpr int CHK = DK / 8, CHV = DV / 8;
@@ -367,7 +376,7 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             size_t off = 0;
             if (ok) {
                 const int pi = page_shift >= 0 ? j >> page_shift : j / page_size, po = j - pi * page_size;
-                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * dv + c * 8;
+                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * v_row + c * 8;
             }
             cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
         }
@@ -414,8 +423,8 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             for (int e = 0; e < 2; ++e) {
                 const int j = kbase + i * 8 + e;
                 const bool vis = j >= key_lo && j < key_hi;
-                s[i][e] = (vis && row_lo_ok) ? s[i][e] * scale_log2 : -INFINITY;
-                s[i][2 + e] = (vis && row_hi_ok) ? s[i][2 + e] * scale_log2 : -INFINITY;
+                s[i][e] = (vis && row_lo_ok) ? as_scored(s[i][e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                s[i][2 + e] = (vis && row_hi_ok) ? as_scored(s[i][2 + e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
                 mx_lo = fmaxf(mx_lo, s[i][e]);
                 mx_hi = fmaxf(mx_hi, s[i][2 + e]);
             }
@@ -552,7 +561,9 @@ static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long o
                        int max_blocks, const int* positions, const int* seq_ids, const int* tile_tok0,
                        const int* tile_ntok, int n_tiles, int H, int Hkv, int dk, int dv, float scale,
                        int window, const float* sinks, int n_splits, float* part_o, float* part_ml,
-                       cudaStream_t stream) {
+                       float softcap, int v_row, cudaStream_t stream) {
+    const float cap_log2 = softcap > 0.f ? softcap * AS_LOG2E : 0.f;
+    const float scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     const size_t smem = ((size_t)AS_BM * (DK + AS_PAD) + 2 * AS_BN * (DK + AS_PAD) + 2 * AS_BN * (DV + AS_PAD)) *
                         sizeof(bf16);
     int rc;
@@ -566,14 +577,15 @@ static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long o
         if (dsm > 48 * 1024) cudaFuncSetAttribute(dec, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
         rc = tgo_launch_pdl(dec, dim3(n_tiles, Hkv, n_splits), dim3(128), dsm, stream, q, q_stride, out,
                             out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions, seq_ids,
-                            H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o, part_ml);
+                            H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o, part_ml,
+                            cap_log2, scale_over_cap, v_row);
     } else {
         auto kernel = attention_sink_kernel<DK, DV>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kernel<<<dim3(n_tiles, Hkv, n_splits), AS_WARPS * 32, smem, stream>>>(
             q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions,
             seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o,
-            part_ml);
+            part_ml, cap_log2, scale_over_cap, v_row);
         rc = launch_status();
     }
     if (rc || n_splits <= 1) return rc;
@@ -593,8 +605,10 @@ TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, lon
                                const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                int n_tiles, int H, int Hkv, int dk, int dv, float scale, int window,
                                const float* sinks, int n_splits, float* part_o, float* part_ml,
-                               cudaStream_t stream) {
+                               float softcap, int v_row, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (v_row <= 0) v_row = dv;
+    if (v_row < dv || (v_row % 8) || !(softcap >= 0.f)) return TGO_E_BAD_ARG;
     if (!tgo_attention_sink_supports(H, Hkv, dk, dv) || page_size <= 0 || max_blocks <= 0 || window < 0 ||
         Hkv > 65535 || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)out % 4) ||
         ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16) || (!tile_tok0) != (!tile_ntok) ||
@@ -605,7 +619,7 @@ TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, lon
                                           (const bf16*)k_cache, (const bf16*)v_cache, page_size,          \
                                           block_tables, max_blocks, positions, seq_ids, tile_tok0,        \
                                           tile_ntok, n_tiles, H, Hkv, dk, dv, scale, window, sinks,   \
-                                          n_splits, part_o, part_ml, stream)
+                                          n_splits, part_o, part_ml, softcap, v_row, stream)
     if (dk <= 64) return dv <= 64 ? AS_GO(64, 64) : AS_GO(64, 128);
     return dv <= 64 ? AS_GO(128, 64) : AS_GO(128, 128);
 #undef AS_GO

@@ -5,11 +5,11 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------ embedding
-// out[t, :] = table[ids[t], :] widened to float32 (the residual stream's type).
+// out[t, :] = table[ids[t], :] * scale, widened to float32 (the residual stream's type).
 // An id outside [0, V) writes zeros; the host refuses such ids before the launch.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int d, int V) {
+                             float* __restrict__ out, int d, int V, float scale) {
     pdl_wait();
     pdl_launch();
     const int t = blockIdx.x;
@@ -17,19 +17,19 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const bool ok = id >= 0 && id < V;
     const T* row = table + (size_t)(ok ? id : 0) * d;
     float* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
 }
 
 TGO_API int tgo_embed(const void* table, int dtype, const int* ids, float* out, int T, int d,
-                      int V, cudaStream_t stream) {
+                      int V, float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream,
-                              (const bf16*)table, ids, out, d, V);
+                              (const bf16*)table, ids, out, d, V, scale);
     else if (dtype == TGO_F32)
         return tgo_launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream,
-                              (const float*)table, ids, out, d, V);
+                              (const float*)table, ids, out, d, V, scale);
     else
         return TGO_E_BAD_ARG;
     return launch_status();
@@ -733,5 +733,116 @@ TGO_API int tgo_qkv_bias_rope_cache(void* q, long long q_stride, void* k, long l
                               (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, H,
                               Hkv, dk, dv, q_bias, k_bias, v_bias, rope, rot, interleaved, slots,
                               (float*)k_cache, (float*)v_cache, page_size);
+    return TGO_E_BAD_ARG;
+}
+
+// ------------------- q and k normed over their WHOLE rows, rotated; k and v into the cache
+// The form of q/k norm that takes all heads of a token as one row: q [H dk] is divided by the
+// root mean square of all its H dk entries and multiplied by a gain of that size (k [Hkv dk]
+// likewise), before the heads are split and rotated. A block a token. Each thread then takes
+// whole rotation pairs (i, i + rot/2, or 2i, 2i + 1 if `interleaved`) and the channels past
+// `rot` singly, so q can be written back in place; k goes to its cache plane
+// [page][kv head][offset][dk], v (untouched) to [page][kv head][offset][dv]. Sums, gains and
+// the rotation are float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rownorm_rope_cache_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k,
+                             long long k_stride, const T* __restrict__ v, long long v_stride, int H,
+                             int Hkv, int dk, int dv, const float* __restrict__ q_gain,
+                             const float* __restrict__ k_gain, float eps,
+                             const float* __restrict__ rope, int rot, int interleaved,
+                             const int* __restrict__ slots, T* __restrict__ k_cache,
+                             T* __restrict__ v_cache, int page_size) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int t = blockIdx.x;
+    T* qr = q + (size_t)t * q_stride;
+    const T* kr = k ? k + (size_t)t * k_stride : nullptr;
+    const int qw = H * dk, kw = Hkv * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < qw; i += blockDim.x) {
+        const float x = to_f32(qr[i]);
+        sq += x * x;
+    }
+    sq = block_sum(sq, scratch);
+    if (kr) {
+        for (int i = threadIdx.x; i < kw; i += blockDim.x) {
+            const float x = to_f32(kr[i]);
+            sk += x * x;
+        }
+        sk = block_sum(sk, scratch);
+    }
+    const float rq = q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f;
+    const float rk = k_gain ? rsqrtf(sk / (float)kw + eps) : 1.f;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    const int half = rot / 2;
+    const float* cs = rope ? rope + (size_t)t * rot : nullptr;
+    const int per_head = dk - half;                      // work items of a head: pairs, then singles
+    const int nq = H * per_head, nk = (kr && slot >= 0) ? Hkv * per_head : 0;
+    for (int w = threadIdx.x; w < nq + nk; w += blockDim.x) {
+        const bool is_q = w < nq;
+        const int ww = is_q ? w : w - nq;
+        const int head = ww / per_head, item = ww % per_head;
+        const T* src = is_q ? qr + (size_t)head * dk : kr + (size_t)head * dk;
+        const float* gain = is_q ? q_gain : k_gain;
+        const float r = is_q ? rq : rk;
+        T* dst = is_q ? qr + (size_t)head * dk
+                      : k_cache + (((size_t)page * Hkv + head) * page_size + off) * dk;
+        if (item < half && cs) {
+            const int a = interleaved ? 2 * item : item, b = interleaved ? 2 * item + 1 : item + half;
+            float xa = to_f32(src[a]) * r, xb = to_f32(src[b]) * r;
+            if (gain) { xa *= gain[head * dk + a]; xb *= gain[head * dk + b]; }
+            const float c = cs[item], sn = cs[half + item];
+            dst[a] = from_f32<T>(xa * c - xb * sn);
+            dst[b] = from_f32<T>(xb * c + xa * sn);
+        } else {
+            // without a table the first `rot` channels are not rotated: items < half stand for
+            // channel pairs that are then written singly
+            if (item < half) {
+                const int a = interleaved ? 2 * item : item, b = interleaved ? 2 * item + 1 : item + half;
+                float xa = to_f32(src[a]) * r, xb = to_f32(src[b]) * r;
+                if (gain) { xa *= gain[head * dk + a]; xb *= gain[head * dk + b]; }
+                dst[a] = from_f32<T>(xa);
+                dst[b] = from_f32<T>(xb);
+            } else {
+                const int i = item + half;
+                float x = to_f32(src[i]) * r;
+                if (gain) x *= gain[head * dk + i];
+                dst[i] = from_f32<T>(x);
+            }
+        }
+    }
+    if (v && slot >= 0) {
+        const T* vr = v + (size_t)t * v_stride;
+        for (int i = threadIdx.x; i < Hkv * dv; i += blockDim.x) {
+            const int head = i / dv, c = i % dv;
+            v_cache[(((size_t)page * Hkv + head) * page_size + off) * dv + c] = vr[i];
+        }
+    }
+}
+
+// q is treated in place; k and v may be null (then only q is); k and v go to the cache only.
+// Gains float32 [H dk] and [Hkv dk], or null for no norm.
+TGO_API int tgo_qk_rownorm_rope_cache(void* q, long long q_stride, const void* k, long long k_stride,
+                                      const void* v, long long v_stride, int dtype, int T, int H,
+                                      int Hkv, int dk, int dv, const float* q_gain,
+                                      const float* k_gain, float eps, const float* rope, int rot,
+                                      int interleaved, const int* slots, void* k_cache,
+                                      void* v_cache, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dk <= 0 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || H <= 0) return TGO_E_BAD_ARG;
+    if ((k || v) && (Hkv <= 0 || page_size <= 0 || !slots || !k_cache)) return TGO_E_BAD_ARG;
+    if (v && !v_cache) return TGO_E_BAD_ARG;
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(qk_rownorm_rope_cache_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)q,
+                              q_stride, (const bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dk, dv,
+                              q_gain, k_gain, eps, rope, rot, interleaved, slots, (bf16*)k_cache,
+                              (bf16*)v_cache, page_size);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(qk_rownorm_rope_cache_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)q,
+                              q_stride, (const float*)k, k_stride, (const float*)v, v_stride, H, Hkv, dk,
+                              dv, q_gain, k_gain, eps, rope, rot, interleaved, slots, (float*)k_cache,
+                              (float*)v_cache, page_size);
     return TGO_E_BAD_ARG;
 }

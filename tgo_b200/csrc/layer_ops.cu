@@ -181,53 +181,62 @@ __device__ __forceinline__ float gate_act(float g, int act) {
     return g / (1.f + expf(-g));
 }
 
+// `bias` (float32 [2f], laid out like a row of gu, or null) is added to the gate and up
+// columns in float32 before the activation.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int f,
-                                 int interleaved, int act) {
+                                 int interleaved, int act, const float* __restrict__ bias) {
     pdl_wait();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= f) return;
     const T* row = gu + (size_t)blockIdx.y * 2 * f;
     const int gi = interleaved ? (j / 8) * 16 + (j % 8) : j;
     const int ui = interleaved ? gi + 8 : f + j;
-    out[(size_t)blockIdx.y * f + j] = from_f32<T>(gate_act(to_f32(row[gi]), act) * to_f32(row[ui]));
+    const float g = to_f32(row[gi]) + (bias ? bias[gi] : 0.f);
+    const float u = to_f32(row[ui]) + (bias ? bias[ui] : 0.f);
+    out[(size_t)blockIdx.y * f + j] = from_f32<T>(gate_act(g, act) * u);
 }
 
 // bfloat16, eight columns a thread (16-byte accesses): needs f % 8 == 0
 __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f,
-                                        int interleaved, int act) {
+                                        int interleaved, int act, const float* __restrict__ bias) {
     pdl_wait();
     const int j8 = blockIdx.x * blockDim.x + threadIdx.x;       // which group of eight columns
     if (j8 * 8 >= f) return;
     const bf16* row = gu + (size_t)blockIdx.y * 2 * f;
-    const uint4 g4 = *(const uint4*)(row + (interleaved ? j8 * 16 : j8 * 8));
-    const uint4 u4 = *(const uint4*)(row + (interleaved ? j8 * 16 + 8 : f + j8 * 8));
+    const int gi = interleaved ? j8 * 16 : j8 * 8, ui = interleaved ? j8 * 16 + 8 : f + j8 * 8;
+    const uint4 g4 = *(const uint4*)(row + gi);
+    const uint4 u4 = *(const uint4*)(row + ui);
     const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
     const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
     uint4 o4;
     __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
-        const float2 g = __bfloat1622float2(g2[x]), u = __bfloat1622float2(u2[x]);
+        float2 g = __bfloat1622float2(g2[x]), u = __bfloat1622float2(u2[x]);
+        if (bias) {
+            g.x += bias[gi + 2 * x]; g.y += bias[gi + 2 * x + 1];
+            u.x += bias[ui + 2 * x]; u.y += bias[ui + 2 * x + 1];
+        }
         o2[x] = __floats2bfloat162_rn(gate_act(g.x, act) * u.x, gate_act(g.y, act) * u.y);
     }
     *(uint4*)(out + (size_t)blockIdx.y * f + j8 * 8) = o4;
 }
 
 TGO_API int tgo_gated_act(const void* gate_up, void* out, int dtype, int T, int f,
-                          int interleaved, int act, cudaStream_t stream) {
+                          int interleaved, int act, const float* bias, cudaStream_t stream) {
     if (T <= 0 || f <= 0) return 0;
     if (act < 0 || act > 2 || (interleaved && f % 8)) return TGO_E_BAD_ARG;
     const dim3 grid((f + 255) / 256, T), block(256);
     if (dtype == TGO_BF16 && f % 8 == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15))
         return tgo_launch_pdl(gated_act_bf16x8_kernel, dim3((f / 8 + 255) / 256, T), block, 0, stream,
-                              (const bf16*)gate_up, (bf16*)out, f, interleaved, act);
+                              (const bf16*)gate_up, (bf16*)out, f, interleaved, act, bias);
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(gated_act_kernel<bf16>, grid, block, 0, stream, (const bf16*)gate_up,
-                              (bf16*)out, f, interleaved, act);
+                              (bf16*)out, f, interleaved, act, bias);
     if (dtype == TGO_F32)
         return tgo_launch_pdl(gated_act_kernel<float>, grid, block, 0, stream,
-                              (const float*)gate_up, (float*)out, f, interleaved, act);
+                              (const float*)gate_up, (float*)out, f, interleaved, act, bias);
     return TGO_E_BAD_ARG;
 }
 
@@ -420,5 +429,78 @@ TGO_API int tgo_scaled_sum(const void* a, float sa, const void* b, float sb, flo
     if (dtype == TGO_F32)
         return tgo_launch_pdl(scaled_sum_kernel<float>, grid, dim3(256), 0, stream, (const float*)a, sa,
                               (const float*)b, sb, out, n);
+    return TGO_E_BAD_ARG;
+}
+
+// -------------------------------- h <- gain * rmsnorm(alpha * h + y + bias)  (+ its copy)
+// The arrangement with the norm AFTER the sum: the stream itself is what the norm leaves. A
+// block a row: the sum s = alpha * h + y (+ bias, float32 [d], a product's bias that was left
+// for here) is kept in shared memory in float32, divided by sqrt(mean s^2 + eps), multiplied
+// by the gain and written back over h; `act`, if given, gets the same values in the
+// activation type for the next sublayer to read.
+template <typename TY, typename TA>
+__global__ void scaled_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y,
+                                       const float* __restrict__ bias, float alpha,
+                                       const float* __restrict__ gain, float eps, int d,
+                                       TA* __restrict__ act) {
+    extern __shared__ float srow[];
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float s = alpha * h[base + i] + to_f32(y[base + i]);
+        if (bias) s += bias[i];
+        srow[i] = s;
+        ss += s * s;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = (srow[i] * r) * gain[i];
+        h[base + i] = v;
+        if (act) act[base + i] = from_f32<TA>(v);
+    }
+}
+
+// h float32 [T, d] (in place); y [T, d] float32 or bfloat16; act bfloat16 [T, d] or null.
+TGO_API int tgo_scaled_add_norm(float* h, const void* y, int y_dtype, const float* bias, float alpha,
+                                const float* gain, float eps, void* act, int T, int d,
+                                cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || (size_t)d * sizeof(float) > 200 * 1024) return TGO_E_BAD_ARG;
+    const int threads = d >= 2048 ? 512 : d >= 512 ? 256 : 128;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (y_dtype == TGO_F32) {
+        auto kern = scaled_add_norm_kernel<float, bf16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(kern, dim3(T), dim3(threads), smem, stream, h, (const float*)y, bias, alpha,
+                              gain, eps, d, (bf16*)act);
+    }
+    if (y_dtype == TGO_BF16) {
+        auto kern = scaled_add_norm_kernel<bf16, bf16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(kern, dim3(T), dim3(threads), smem, stream, h, (const bf16*)y, bias, alpha,
+                              gain, eps, d, (bf16*)act);
+    }
+    return TGO_E_BAD_ARG;
+}
+
+// ----------------------------------------------------------------- y += bias, row by row
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, int d, size_t n) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = from_f32<T>(to_f32(y[i]) + bias[i % d]);
+}
+
+TGO_API int tgo_add_bias(void* y, int dtype, const float* bias, int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0) return 0;
+    const size_t n = (size_t)T * d;
+    const dim3 grid((unsigned)((n + 255) / 256)), block(256);
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(add_bias_kernel<bf16>, grid, block, 0, stream, (bf16*)y, bias, d, n);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(add_bias_kernel<float>, grid, block, 0, stream, (float*)y, bias, d, n);
     return TGO_E_BAD_ARG;
 }

@@ -163,7 +163,10 @@ class Model:
         """Run the step's tokens through every call; logits (float32) at ctx.logit_rows."""
         s = self.spec
         h = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
-        ops.embed(self.embedding, ctx.token_ids, h)
+        if s.embedding_scale != 1.0:
+            ops.embed(self.embedding, ctx.token_ids, h, float(s.embedding_scale))
+        else:
+            ops.embed(self.embedding, ctx.token_ids, h)
         pending = None
         for ci, call in enumerate(s.run_order):
             cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)

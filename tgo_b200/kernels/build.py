@@ -32,6 +32,8 @@ LIBRARIES = {
     "attention_generic": (["attention_generic.cu"], []),
     "attention_mixed": (["attention_mixed.cu"], []),
     "retention": (["retention.cu"], []),
+    "mlstm": (["mlstm.cu"], []),
+    "latent": (["latent.cu"], []),
     "layer_ops": (["layer_ops.cu"], []),
     "state_space": (["state_space.cu"], []),
     "attention_sink": (["attention_sink.cu"], []),

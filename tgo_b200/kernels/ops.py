@@ -58,14 +58,14 @@ def _check(status: int, name: str, detail: str = "") -> None:
     raise KernelError(f"{name}: CUDA error {status} at launch {detail}")
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] widened to float32. ids int32 [T]; out float32 [T, d]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale, widened to float32. ids int32 [T]; out float32 [T, d]."""
     _need_cuda(table, ids, out)
     T, d = out.shape
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
     lib = load_library("elementwise")
     _check(lib.tgo_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out),
-                         c_int(T), c_int(d), c_int(table.shape[0]), _stream()), "embed")
+                         c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()), "embed")
 
 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
@@ -162,11 +162,15 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                       block_tables: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
                       scale: float, window: int, value_dim: Optional[int] = None,
-                      sinks: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                      value_row: int = 0) -> None:
     """Paged causal attention, one warp per (token, head). q is a 2-D view [T, >= H*dh]
     with unit column stride; out likewise. window 0 = every earlier key. `value_dim`: width
     of a value row where it differs from the keys'; `sinks`: float32 [H], a term exp(sink_h)
-    in each head's softmax denominator that has no value."""
+    in each head's softmax denominator that has no value; `softcap` c > 0: every scaled score
+    goes through c tanh(s / c); `value_row`: elements from one value row to the next where
+    that is not `value_dim` (values that are the first channels of their key rows: v_cache is
+    k_cache and value_row the key rows' width)."""
     _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads and
                              sinks.is_contiguous())
@@ -181,7 +185,8 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
         c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(value_dim or head_dim), _ptr(k_cache),
         _ptr(v_cache), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
-        _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _ptr(sinks), _stream()),
+        _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _ptr(sinks),
+        c_float(softcap or 0.0), c_int(value_row), _stream()),
         "attention_generic", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
 
 
@@ -239,17 +244,48 @@ def softcap(x: torch.Tensor, cap: float) -> None:
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool, activation: str) -> None:
-    """out[t, j] = act(gate_j) * up_j, the columns laid out as for `swiglu`."""
-    _need_cuda(gate_up, out)
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool, activation: str,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """out[t, j] = act(gate_j) * up_j, the columns laid out as for `swiglu`; `bias` (float32
+    [2f], laid out like a row of gate_up) is added to both in float32 first."""
+    _need_cuda(gate_up, out, bias)
     T, f = out.shape
     assert gate_up.shape == (T, 2 * f) and gate_up.is_contiguous() and out.is_contiguous()
     assert gate_up.dtype == out.dtype
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * f and
+                            bias.is_contiguous())
     lib = load_library("layer_ops")
     _check(lib.tgo_gated_act(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T),
                              c_int(f), c_int(1 if interleaved else 0),
-                             c_int(ACTIVATIONS[activation]), _stream()), "gated_act",
+                             c_int(ACTIVATIONS[activation]), _ptr(bias), _stream()), "gated_act",
            f"(T={T}, f={f}, {activation})")
+
+
+def scaled_add_norm(h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor], alpha: float,
+                    gain: torch.Tensor, eps: float, act: Optional[torch.Tensor] = None) -> None:
+    """h <- gain * rmsnorm(alpha * h + y + bias), the float32 stream h in place; y float32 or
+    bfloat16 [T, d]; bias float32 [d] or None; `act` (bfloat16) also gets the new stream."""
+    _need_cuda(h, y, bias, gain, act)
+    T, d = h.shape
+    assert h.dtype == torch.float32 and h.is_contiguous() and y.shape == h.shape
+    assert y.is_contiguous() and gain.dtype == torch.float32 and gain.numel() == d
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == d)
+    assert act is None or (act.dtype == torch.bfloat16 and act.shape == h.shape and
+                           act.is_contiguous())
+    lib = load_library("layer_ops")
+    _check(lib.tgo_scaled_add_norm(_ptr(h), _ptr(y), c_int(dtype_code(y.dtype)), _ptr(bias),
+                                   c_float(alpha), _ptr(gain), c_float(eps), _ptr(act), c_int(T),
+                                   c_int(d), _stream()), "scaled_add_norm", f"(d={d})")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[t] += bias, the sum in float32; y [T, d] in either storage type, bias float32 [d]."""
+    _need_cuda(y, bias)
+    T, d = y.shape
+    assert y.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == d
+    lib = load_library("layer_ops")
+    _check(lib.tgo_add_bias(_ptr(y), c_int(dtype_code(y.dtype)), _ptr(bias), c_int(T), c_int(d),
+                            _stream()), "add_bias")
 
 
 def value_norm_share_cache(v: torch.Tensor, num_kv_heads: int, value_dim: int, norm: bool,
@@ -337,8 +373,10 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
                         page_size: int, block_tables: torch.Tensor, seq_ids: torch.Tensor,
                         positions: torch.Tensor, scale: float, window: int,
                         sinks: Optional[torch.Tensor], tile_tok0: Optional[torch.Tensor] = None,
-                        tile_ntok: Optional[torch.Tensor] = None, n_splits: int = 1) -> None:
-    """Paged causal attention with keys `key_dim` and values `value_dim` wide, a window (0:
+                        tile_ntok: Optional[torch.Tensor] = None, n_splits: int = 1,
+                        softcap: float = 0.0, value_row: int = 0) -> None:
+    """`softcap` and `value_row` as in `attention_generic`.
+    Paged causal attention with keys `key_dim` and values `value_dim` wide, a window (0:
     none) and a sink per head (float32 [H] or None), bfloat16 on the tensor cores: a block per
     tile of consecutive tokens of one request (tile_tok0, tile_ntok: int32; None: every token
     is a tile of its own) and kv head. Without tile lists, `n_splits` > 1 cuts every token's
@@ -366,7 +404,8 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
         c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), c_float(scale), c_int(window),
-        _ptr(sinks), c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()), "attention_sink",
+        _ptr(sinks), c_int(n_splits), _ptr(part_o), _ptr(part_ml), c_float(softcap or 0.0),
+        c_int(value_row), _stream()), "attention_sink",
         f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
     if n_splits > 1:
         LAUNCHES[0] += 1
@@ -432,6 +471,147 @@ def qkv_bias_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[
         c_int(1 if interleaved else 0), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _stream()), "qkv_bias_rope_cache",
         f"(dk={key_dim}, dv={value_dim}, rotary_dim={rotary_dim})")
+
+
+def qk_rownorm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+                          num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                          q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                          rope: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                          slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], page_size: int) -> None:
+    """Projection rows of an attention whose q/k norm takes a token's WHOLE q row (all heads,
+    num_heads * key_dim entries, a gain of that size) and whole k row at once: RMS norm in
+    float32, then the first `rotary_dim` channels of every head rotated by `rope` (either
+    pairing); q written back in place, k and v stored at `slots` of their cache planes
+    [page, kv head, offset, width]. q, k, v are 2-D views with unit column stride."""
+    _need_cuda(q, k, v, q_gain, k_gain, rope, slots, k_cache, v_cache)
+    T = q.shape[0]
+    for t in (q, k, v):
+        if t is not None:
+            assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    for g, n in ((q_gain, num_heads * key_dim), (k_gain, num_kv_heads * key_dim)):
+        assert g is None or (g.dtype == torch.float32 and g.numel() == n and g.is_contiguous())
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    if k is not None:
+        assert k_cache is not None and k_cache.dtype == q.dtype and k_cache.is_contiguous()
+        assert slots.dtype == torch.int32 and slots.numel() == T
+    if v is not None:
+        assert v_cache is not None and v_cache.dtype == q.dtype and v_cache.is_contiguous()
+    lib = load_library("elementwise")
+    _check(lib.tgo_qk_rownorm_rope_cache(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0) if k is not None else 0),
+        _ptr(v), c_ll(v.stride(0) if v is not None else 0), c_int(dtype_code(q.dtype)), c_int(T),
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _ptr(q_gain),
+        _ptr(k_gain), c_float(eps), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
+        c_int(1 if interleaved else 0), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _stream()), "qk_rownorm_rope_cache",
+        f"(dk={key_dim}, dv={value_dim}, rotary_dim={rotary_dim})")
+
+
+def mlstm_state_floats(num_heads: int, key_dim: int, value_dim: int) -> int:
+    """Floats of one request's state row: S [H, dk, dv], then n [H, dk], then m [H]."""
+    return num_heads * key_dim * value_dim + num_heads * key_dim + num_heads
+
+
+def mlstm(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate_i: torch.Tensor,
+          gate_f: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+          q_scale: float, out: torch.Tensor, num_seqs: int, num_heads: int, key_dim: int,
+          value_dim: int, q_start: torch.Tensor, state_slots: torch.Tensor,
+          state: torch.Tensor) -> None:
+    """The matrix memory with exponential gates over a step's tokens, request by request and
+    in order, from and to `state` (float32 [slots, mlstm_state_floats]): q, k [T, H dk] and v
+    [T, H dv] are 2-D views in the activation type; gate_i, gate_f float32 views [T, H] (the
+    gate projections' rows, of one row stride) with their biases float32 [H]; log input gate
+    cap tanh((a + b) / cap), log forget gate logsigmoid of the same form; q times q_scale;
+    out float32 [T, H dv], the memory's read-out divided by its denominator."""
+    _need_cuda(q, k, v, gate_i, gate_f, bias_i, bias_f, out, q_start, state_slots, state)
+    T = q.shape[0]
+    for t in (q, k, v):
+        assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    assert gate_i.dtype == gate_f.dtype == torch.float32 and gate_i.shape == gate_f.shape == (T, num_heads)
+    assert gate_i.stride(1) == gate_f.stride(1) == 1 and gate_i.stride(0) == gate_f.stride(0)
+    assert bias_i.dtype == bias_f.dtype == torch.float32 and bias_i.numel() == bias_f.numel() == num_heads
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, num_heads * value_dim)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+    assert q_start.dtype == torch.int32 and state_slots.dtype == torch.int32
+    rec = torch.empty((T, num_heads, 4), dtype=torch.float32, device=q.device)
+    m_first = torch.empty((num_seqs, num_heads), dtype=torch.float32, device=q.device)
+    lib = load_library("mlstm")
+    _check(lib.tgo_mlstm(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
+        c_int(dtype_code(q.dtype)), _ptr(gate_i), _ptr(gate_f), c_ll(gate_i.stride(0)), _ptr(bias_i),
+        _ptr(bias_f), c_float(cap), c_float(q_scale), _ptr(out), c_int(num_seqs), c_int(num_heads),
+        c_int(key_dim), c_int(value_dim), _ptr(q_start), _ptr(state_slots), _ptr(state),
+        c_ll(state.shape[1]), _ptr(rec), _ptr(m_first), _stream()), "mlstm",
+        f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
+    LAUNCHES[0] += 1
+
+
+def latent_row_cache(kv: torch.Tensor, rank: int, width: int, gain: torch.Tensor, eps: float,
+                     rope: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                     slots: torch.Tensor, cache: torch.Tensor, page_size: int) -> None:
+    """The cache row of a latent attention: kv [T, rank + width] (a 2-D view): the first
+    `rank` channels RMS-normed with `gain`, of the last `width` the first `rotary_dim` rotated
+    by `rope`; stored at `slots` of the plane [page, 1, offset, rank + width]."""
+    _need_cuda(kv, gain, rope, slots, cache)
+    T = kv.shape[0]
+    assert kv.stride(1) == 1 and kv.shape[1] == rank + width and cache.dtype == kv.dtype
+    assert cache.is_contiguous() and cache.shape[-1] == rank + width and cache.shape[-2] == page_size
+    assert cache.numel() == cache.shape[0] * page_size * (rank + width)
+    assert gain.dtype == torch.float32 and gain.numel() == rank and slots.dtype == torch.int32
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    lib = load_library("latent")
+    _check(lib.tgo_latent_row_cache(
+        _ptr(kv), c_ll(kv.stride(0)), c_int(dtype_code(kv.dtype)), c_int(T), c_int(rank), c_int(width),
+        _ptr(gain), c_float(eps), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
+        c_int(1 if interleaved else 0), _ptr(slots), _ptr(cache), c_int(page_size), _stream()),
+        "latent_row_cache", f"(rank={rank}, width={width})")
+
+
+def rope_slice(src: torch.Tensor, src_head: int, src_off: int, dst: torch.Tensor, dst_head: int,
+               dst_off: int, num_heads: int, width: int, rope: Optional[torch.Tensor],
+               rotary_dim: int, interleaved: bool) -> None:
+    """dst[t, h * dst_head + dst_off + i] = src[t, h * src_head + src_off + i] for i < width,
+    the first `rotary_dim` of those channels rotated by `rope` (either pairing)."""
+    _need_cuda(src, dst, rope)
+    T = src.shape[0]
+    assert src.stride(1) == 1 and dst.stride(1) == 1 and src.dtype == dst.dtype and dst.shape[0] == T
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    lib = load_library("latent")
+    _check(lib.tgo_rope_slice(
+        _ptr(src), c_ll(src.stride(0)), c_int(src_head), c_int(src_off), _ptr(dst),
+        c_ll(dst.stride(0)), c_int(dst_head), c_int(dst_off), c_int(dtype_code(src.dtype)), c_int(T),
+        c_int(num_heads), c_int(width), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
+        c_int(1 if interleaved else 0), _stream()), "rope_slice")
+
+
+HEAD_LINEAR_LIBRARY_ROWS = 65     # bfloat16 steps of this many rows or more: the library's
+                                  # batched product
+
+
+def head_linear(x: torch.Tensor, x_head: int, w: torch.Tensor, y: torch.Tensor, y_head: int) -> None:
+    """A product per head: y[t, h * y_head + n] = sum_k x[t, h * x_head + k] w[h, n, k], with
+    w [H, N, K]; x and y 2-D views with unit column stride. float32, and bfloat16 with few
+    rows: this package's kernel (k summed in order); bfloat16 with many rows: the library's
+    batched product, where the dense products of as many rows take the library too."""
+    _need_cuda(x, w, y)
+    T = x.shape[0]
+    H, N, K = w.shape
+    assert w.is_contiguous() and x.stride(1) == 1 and y.stride(1) == 1
+    assert x.dtype == w.dtype == y.dtype and y.shape[0] == T
+    if x.dtype == torch.bfloat16 and T >= HEAD_LINEAR_LIBRARY_ROWS:
+        xv = torch.as_strided(x, (H, T, K), (x_head, x.stride(0), 1))
+        yv = torch.as_strided(y, (H, T, N), (y_head, y.stride(0), 1))
+        yv.copy_(torch.bmm(xv, w.transpose(1, 2)))
+        return
+    lib = load_library("latent")
+    _check(lib.tgo_head_linear(_ptr(x), c_ll(x.stride(0)), c_int(x_head), _ptr(w), _ptr(y),
+                               c_ll(y.stride(0)), c_int(y_head), c_int(dtype_code(x.dtype)), c_int(T),
+                               c_int(H), c_int(N), c_int(K), _stream()), "head_linear",
+           f"(H={H}, N={N}, K={K})")
 
 
 def causal_conv_act(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor,
@@ -920,17 +1100,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool,
-                 activation: str = "silu") -> torch.Tensor:
+                 activation: str = "silu", bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
     in turn, which lets the bfloat16 kernels apply the gate in their epilogue. The product
-    kernels' epilogues know SiLU; another activation takes the product, then the gate kernel."""
+    kernels' epilogues know SiLU; another activation, or a `bias` (float32 [2f] in the rows'
+    order), takes the product, then the gate kernel."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
-    if activation != "silu":
+    if activation != "silu" or bias is not None:
         x = rows_of(x)
         gu = linear(x, w_gate_up)
         out = torch.empty((M, f), dtype=x.dtype, device=x.device)
-        gated_act(gu, out, interleaved, activation)
+        gated_act(gu, out, interleaved, activation, bias)
         return out
     if isinstance(x, NormedRows):
         if interleaved and _skinny_ok(x, w_gate_up) and folds_norm(M, 2 * f, w_gate_up.shape[1]):

@@ -7,14 +7,17 @@
   - `window`: a query reads itself and the window - 1 keys before it;
   - `sink`: one learned number per query head joins the softmax's denominator as exp(sink_h);
     the term stands for no token (nothing is read for it and nothing added to the output)
-    and enters unscaled, a single time.
+    and enters unscaled, a single time;
+  - `qk_norm` with scope "row": q and k are RMS-normed over a token's whole projection row
+    (all heads at once, gains as wide as the rows), before the heads are split and rotated;
+  - `softcap` c: every scaled score goes through c tanh(score / c) before the softmax.
 
     score(i, j) = (q_i . k_j) * scale       for 0 <= i - j < window
     w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))
     out_i       = Wo concat_h sum_j w_h(i, j) v_kv(h)(j)
 
 Scores, softmax and sums are float32. Tensor roles: q, k, v, o and, with `bias`, q_bias, k_bias,
-v_bias; with `sink`, sink.
+v_bias; with `sink`, sink; with the row norm, q_norm, k_norm.
 """
 from __future__ import annotations
 
@@ -43,15 +46,24 @@ class SinkAttention(Part):
         self.window = spec.window
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(self.dk)
         self.bias, self.sink = bool(spec.bias), bool(spec.sink)
+        self.softcap = float(spec.softcap) if getattr(spec, "softcap", None) else 0.0
+        self.row_norm = bool(spec.qk_norm)
+        if self.row_norm and getattr(spec, "qk_norm_scope", "head") != "row":
+            raise ValueError("attention: this mixer norms q and k over whole rows (qk_norm_scope "
+                             "'row'); the per-head norm belongs to gqa_attention")
+        if self.row_norm and self.bias:
+            raise ValueError("attention: biased projections with a q/k norm are not offered")
+        self.eps = float(spec.norm_eps)
         pos = spec.position
         self.position = POSITIONS.get(pos.kind)(pos, self.dk, device) if pos is not None else None
         if self.position is not None and not hasattr(self.position, "table"):
             raise ValueError("attention: this mixer rotates inside its own kernel and needs a "
                              "position encoding that offers a table of cosines and sines")
         roles = ["q", "k", "v", "o"] + (["q_bias", "k_bias", "v_bias"] if self.bias else []) + \
-            (["sink"] if self.sink else [])
+            (["sink"] if self.sink else []) + (["q_norm", "k_norm"] if self.row_norm else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "attention")
         self.w_qkv = self.w_o = self.b_q = self.b_k = self.b_v = self.sinks = None
+        self.q_gain = self.k_gain = None
 
     def weight_specs(self):
         n, d = self.names, self.hidden
@@ -63,6 +75,8 @@ class SinkAttention(Part):
                     WeightSpec(n["v_bias"], (vw,), "gain")]
         if self.sink:
             out.append(WeightSpec(n["sink"], (self.H,), "gain"))
+        if self.row_norm:
+            out += [WeightSpec(n["q_norm"], (qw,), "gain"), WeightSpec(n["k_norm"], (kw,), "gain")]
         return out
 
     def cache_need(self):
@@ -81,6 +95,9 @@ class SinkAttention(Part):
                                             for r in ("q_bias", "k_bias", "v_bias"))
         if self.sink:
             self.sinks = weights.pop(n["sink"]).to(torch.float32).contiguous()
+        if self.row_norm:
+            self.q_gain = weights.pop(n["q_norm"]).to(torch.float32).contiguous()
+            self.k_gain = weights.pop(n["k_norm"]).to(torch.float32).contiguous()
 
     def libraries(self, dtype, page_size) -> List[str]:
         names = ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise",
@@ -120,34 +137,44 @@ class SinkAttention(Part):
         if self.position is not None:
             table, rot = self.position.table(ctx), self.position.rotary_dim
             interleaved = getattr(self.position, "pairing", "half_split") == "interleaved"
-        ops.qkv_bias_rope_cache(q, k, v, H, Hkv, dk, dv, self.b_q, self.b_k, self.b_v, table, rot,
-                                interleaved, cache.slots, cache.k, cache.v, cache.page_size)
+        if self.row_norm:
+            ops.qk_rownorm_rope_cache(q, k, v, H, Hkv, dk, dv, self.q_gain, self.k_gain, self.eps,
+                                      table, rot, interleaved, cache.slots, cache.k, cache.v,
+                                      cache.page_size)
+        else:
+            ops.qkv_bias_rope_cache(q, k, v, H, Hkv, dk, dv, self.b_q, self.b_k, self.b_v, table,
+                                    rot, interleaved, cache.slots, cache.k, cache.v, cache.page_size)
         a = torch.empty((x.shape[0], H * dv), dtype=q.dtype, device=q.device)
-        sink_attention(q, a, H, Hkv, dk, dv, cache, ctx, self.scale, self.window or 0, self.sinks)
+        sink_attention(q, a, H, Hkv, dk, dv, cache, ctx, self.scale, self.window or 0, self.sinks,
+                       softcap=self.softcap)
         return ops.linear(a, self.w_o, out_dtype=self.out_dtype)
 
 
 USE_TILE_KERNELS = True
 
 
-def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks) -> None:
-    """Which kernel runs the attention of a step. bfloat16 at sizes the tensor-core kernel
+def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, softcap=0.0,
+                   value_row=0) -> None:
+    """`softcap` bounds the scores; `value_row` > 0 says that a value is the first dv channels
+    of its key row, `value_row` wide (one cache plane serves as keys and values).
+    Which kernel runs the attention of a step. bfloat16 at sizes the tensor-core kernel
     takes: that kernel, over tiles of consecutive tokens for steps with prompt portions (single
     tokens beside them are tiles of one), a tile a token for steps of single tokens, whose keys
     may be cut over several blocks. float32,
     and other sizes: the generic kernel (a warp per token and head, keys in a fixed order)."""
-    if USE_TILE_KERNELS and q.dtype == torch.bfloat16 and \
+    v_cache = cache.k if value_row else cache.v
+    if USE_TILE_KERNELS and q.dtype == torch.bfloat16 and value_row % 8 == 0 and \
             ops.attention_sink_supports(H, Hkv, dk, dv) and ops.attention_sink_takes(q, out):
         tok0, ntok = (None, None) if ctx.decode_only else \
             step_tiles(ctx, ops.attention_sink_tile_tokens(H // Hkv))
         splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
-        ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, cache.v, cache.page_size,
+        ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, v_cache, cache.page_size,
                                 cache.block_tables, ctx.seq_ids, ctx.positions, scale, window, sinks,
-                                tok0, ntok, n_splits=splits)
+                                tok0, ntok, n_splits=splits, softcap=softcap, value_row=value_row)
         return
-    ops.attention_generic(q, out, H, Hkv, dk, cache.k, cache.v, cache.page_size,
+    ops.attention_generic(q, out, H, Hkv, dk, cache.k, v_cache, cache.page_size,
                           cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
-                          value_dim=dv, sinks=sinks)
+                          value_dim=dv, sinks=sinks, softcap=softcap, value_row=value_row)
 
 
 MIXERS.register("sink_attention", SinkAttention)

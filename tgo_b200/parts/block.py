@@ -5,7 +5,9 @@
 (model/qwen3_graph.go:76-100). The residual stream h is float32. Each add is left
 pending and handed to the next norm, which does it in its own kernel. The two norms'
 checkpoint names come from the layer spec's `tensors` table (roles mixer_norm, ffn_norm).
-The second, `PostNormScaledResidual` below, norms and scales each sublayer's output instead.
+The second, `PostNormScaledResidual` below, norms and scales each sublayer's output instead;
+the third norms a sublayer's input and its output; the fourth, `PostNormResidual`, norms the
+sum, so that the stream itself is what the norm leaves.
 """
 from __future__ import annotations
 
@@ -276,3 +278,95 @@ class SandwichNormResidual(Part):
 
 
 BLOCKS.register("sandwich_norm_residual", SandwichNormResidual)
+
+
+class PostNormResidual(Part):
+    """Arrangement with the norm AFTER the sum (post-LN), the stream scaled before it:
+
+        h = norm1(a * h + mixer(h));  h = norm2(a * h + feed_forward(h))
+
+    with a = the layer spec's `residual_scale`. The sublayers read the stream itself (in a
+    bfloat16 engine the copy that the norm's kernel writes beside the float32 stream); the
+    sum, the norm and the stream are float32. A layer may have no feed-forward (it then has
+    no second norm). A sublayer that offers `output_bias` (its last product's bias, left
+    unadded when the block sets `defer_output_bias`) has it added in the norm's kernel.
+    Tensor roles of the layer spec: mixer_norm, ffn_norm."""
+
+    STREAM_KEY = PostNormScaledResidual.STREAM_KEY
+
+    def __init__(self, spec: LayerSpec, hidden: int, device=None):
+        p = spec.prefix
+        has_ffn = spec.feed_forward is not None
+        roles = ["mixer_norm"] + (["ffn_norm"] if has_ffn else [])
+        self.names = tensor_names(spec.tensors, p, roles, "post-norm block")
+        self.alpha = float(spec.residual_scale)
+        make = NORMS.get(spec.norm.kind)
+        self.norm1 = make(spec.norm, hidden, self.names["mixer_norm"])
+        if not hasattr(self.norm1, "scaled_add_norm"):
+            raise ValueError(f"post-norm block: the norm {spec.norm.kind!r} cannot norm the "
+                             "stream in place (no scaled_add_norm)")
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
+        self.norm2 = self.feed_forward = None
+        if has_ffn:
+            self.norm2 = make(spec.norm, hidden, self.names["ffn_norm"])
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
+                spec.feed_forward, hidden, p, device)
+        for part in (self.mixer, self.feed_forward):
+            if part is None:
+                continue
+            if hasattr(part, "out_dtype"):
+                part.out_dtype = torch.float32      # the sum that follows is float32
+            if hasattr(part, "defer_output_bias"):
+                part.defer_output_bias = True       # added in the norm's kernel
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def weight_specs(self):
+        out = []
+        for part in self.parts():
+            out += part.weight_specs()
+        return out
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def libraries(self, dtype, page_size):
+        out = ["layer_ops"]
+        for part in self.parts():
+            out += offered(part, "libraries")(dtype, page_size)
+        return out
+
+    def prepare_capture(self, ctx, cache):
+        for part in self.parts():
+            offered(part, "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, writes_cache=True):
+        return sum(offered(part, "flops")(extents, first_positions, writes_cache)
+                   for part in self.parts())
+
+    def cache_bytes_read(self, context_len, width):
+        return offered(self.mixer, "cache_bytes_read")(context_len, width)
+
+    _rows = PostNormScaledResidual._rows
+
+    def _norm(self, norm, h, y, part, ctx):
+        act = None
+        if ctx.act_dtype != torch.float32:
+            act = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+        norm.scaled_add_norm(h, y, getattr(part, "output_bias", None), self.alpha, act)
+        ctx.aux[self.STREAM_KEY] = (h, act)
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.aux.pop(self.STREAM_KEY, None)
+        self._norm(self.norm1, h, self.mixer.forward(self._rows(h, ctx), ctx, cache), self.mixer, ctx)
+        if self.feed_forward is not None:
+            self._norm(self.norm2, h, self.feed_forward.forward(self._rows(h, ctx), ctx),
+                       self.feed_forward, ctx)
+        return h, None
+
+
+BLOCKS.register("postnorm_residual", PostNormResidual)

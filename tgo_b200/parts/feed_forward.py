@@ -1,5 +1,6 @@
-"""Dense gated feed-forward: (act(x Wg^T) * (x Wu^T)) Wd^T, no bias, act = SiLU unless the
-spec names another activation (nn/blocks.go:57-66). The gate and up matrices are joined at bind time so that one
+"""Dense gated feed-forward: (act(x Wg^T) * (x Wu^T)) Wd^T, act = SiLU unless the
+spec names another activation (nn/blocks.go:57-66); without biases unless the spec's `bias` is
+set, then (act(x Wg^T + bg) * (x Wu^T + bu)) Wd^T + bd (roles gate_bias, up_bias, down_bias). The gate and up matrices are joined at bind time so that one
 matrix product makes both, and one kernel applies the gate. The checkpoint names of the
 three matrices come from the spec's `tensors` table (roles gate, up or gate_up for a
 matrix that is shipped joined, gate rows first; down)."""
@@ -25,11 +26,17 @@ class SwiGLU(Part):
             raise ValueError(f"feed-forward: activation {self.activation!r}; known: "
                              f"{sorted(ops.ACTIVATIONS)}")
         self.joined = "gate_up" in dict(spec.tensors)
-        roles = (["gate_up"] if self.joined else ["gate", "up"]) + ["down"]
+        self.bias = bool(getattr(spec, "bias", False))
+        if self.bias and self.joined:
+            raise ValueError("feed-forward: biases come with separate gate and up matrices")
+        roles = (["gate_up"] if self.joined else ["gate", "up"]) + ["down"] + \
+            (["gate_bias", "up_bias", "down_bias"] if self.bias else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "feed-forward")
         self.w_gate_up = None
         self.w_down = None
         self.interleaved = False
+        self.b_gate_up = None            # float32 [2 ff], in the order of w_gate_up's rows
+        self.output_bias = None          # float32 [hidden]: the down product's bias
 
     def weight_specs(self):
         n = self.names
@@ -38,7 +45,12 @@ class SwiGLU(Part):
         else:
             first = [WeightSpec(n["gate"], (self.inter, self.hidden)),
                      WeightSpec(n["up"], (self.inter, self.hidden))]
-        return first + [WeightSpec(n["down"], (self.hidden, self.inter))]
+        out = first + [WeightSpec(n["down"], (self.hidden, self.inter))]
+        if self.bias:
+            out += [WeightSpec(n["gate_bias"], (self.inter,), "gain"),
+                    WeightSpec(n["up_bias"], (self.inter,), "gain"),
+                    WeightSpec(n["down_bias"], (self.hidden,), "gain")]
+        return out
 
     def bind(self, weights):
         n = self.names
@@ -57,9 +69,18 @@ class SwiGLU(Part):
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights.pop(n["down"]).contiguous()
+        if self.bias:
+            bg = weights.pop(n["gate_bias"]).to(torch.float32)
+            bu = weights.pop(n["up_bias"]).to(torch.float32)
+            if self.interleaved:
+                self.b_gate_up = torch.stack([bg.reshape(f // 8, 8), bu.reshape(f // 8, 8)],
+                                             dim=1).reshape(2 * f).contiguous()
+            else:
+                self.b_gate_up = torch.cat([bg, bu]).contiguous()
+            self.output_bias = weights.pop(n["down_bias"]).to(torch.float32).contiguous()
 
     def libraries(self, dtype, page_size) -> List[str]:
-        extra = ["layer_ops"] if self.activation != "silu" else []
+        extra = ["layer_ops"] if self.activation != "silu" or self.bias else []
         return (["sgemm"] if dtype == torch.float32 else ["gemm_skinny"]) + extra
 
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
@@ -70,6 +91,16 @@ class SwiGLU(Part):
     def forward(self, x, ctx, residual=None):
         """With `residual` (the float32 stream) the result may be added to it, and None is
         then returned; otherwise the result is returned for the caller to add."""
+        if self.bias:
+            act = ops.gated_linear(x, self.w_gate_up, self.interleaved, self.activation,
+                                   bias=self.b_gate_up)
+            y = ops.linear(act, self.w_down, out_dtype=self.out_dtype)
+            if not self.defer_output_bias:
+                ops.add_bias(y, self.output_bias)
+            if residual is not None:
+                ops.residual_add(residual, y)
+                return None
+            return y
         if self.activation == "silu":
             act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
         else:
@@ -77,6 +108,7 @@ class SwiGLU(Part):
         return ops.linear(act, self.w_down, residual=residual, out_dtype=self.out_dtype)
 
     out_dtype = None        # a block that norms the result in float32 asks for float32 rows
+    defer_output_bias = False   # a block that adds `output_bias` itself sets this
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -51,6 +51,12 @@ class RMSNorm(Part):
         ops.add_rmsnorm(h, delta, self.gain, self.eps, out, rows)
         return out
 
+    def scaled_add_norm(self, h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor],
+                        alpha: float, act: Optional[torch.Tensor] = None) -> None:
+        """h <- gain * norm(alpha * h + y + bias): the stream itself is normed, in place, for
+        blocks that norm AFTER the sum; `act` also gets the new stream in the activation type."""
+        ops.scaled_add_norm(h, y, bias, alpha, self.gain, self.eps, act)
+
 
 class GroupRMSNorm(Part):
     """RMSNorm in groups: the row is cut into `groups` equal consecutive parts, each divided by
@@ -91,6 +97,13 @@ class GroupRMSNorm(Part):
         """h += scale * gain * norm(y), the stream h in float32; `act` also gets the new
         stream in the activation type."""
         ops.group_norm_scale_add(h, y, self.gain, scale, self.eps, self.groups, act)
+
+    def scaled_add_norm(self, h: torch.Tensor, y: torch.Tensor, bias: Optional[torch.Tensor],
+                        alpha: float, act: Optional[torch.Tensor] = None) -> None:
+        """h <- gain * norm(alpha * h + y + bias), in place (one group only)."""
+        if self.groups != 1:
+            raise ValueError("group norm: the norm of the stream itself is not grouped")
+        ops.scaled_add_norm(h, y, bias, alpha, self.gain, self.eps, act)
 
 
 NORMS.register("rmsnorm", RMSNorm)

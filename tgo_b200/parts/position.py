@@ -102,6 +102,37 @@ class RopeInterleaved(RopeHalfSplit):
                                         None, table, self.rotary_dim, True, None, None, None, 0)
 
 
+class RopeStretchedInterleaved(RopeStretched):
+    """The stretched rotation (ramp over the pairs, enlarged cosines and sines) with
+    neighbouring channels paired: pair i is channels 2i and 2i + 1."""
+    fusable = False
+    pairing = "interleaved"
+
+    def apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim):
+        RopeInterleaved.apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim)
+
+
+class RopeBanded(RopeHalfSplit):
+    """The half-split rotation slowed by wavelength bands (the scheme Llama 3.1 uses):
+    `scaling` = (factor, low, high, original). With f_i = theta^(-2i/rot) and the wavelength
+    l_i = 2 pi / f_i: short waves, l_i < original / high, keep f_i; long waves, l_i > original
+    / low, get f_i / factor; between them, with s = (original / l_i - low) / (high - low), the
+    frequency is (1 - s) f_i / factor + s f_i."""
+
+    def frequencies(self, spec: PositionSpec, rot: int) -> torch.Tensor:
+        import math
+        base = super().frequencies(spec, rot)
+        if not spec.scaling:
+            return base
+        factor, low, high, original = (float(x) for x in spec.scaling)
+        wave = 2.0 * math.pi / base
+        s = (original / wave - low) / (high - low) if high != low else torch.ones_like(wave)
+        out = (1.0 - s) * base / factor + s * base
+        out = torch.where(wave < original / high, base, out)
+        out = torch.where(wave > original / low, base / factor, out)
+        return out
+
+
 class NoPosition(Part):
     """Positions do not enter the mixer."""
     fusable = True
@@ -119,4 +150,6 @@ class NoPosition(Part):
 POSITIONS.register("rope_half_split", RopeHalfSplit)
 POSITIONS.register("rope_stretched", RopeStretched)
 POSITIONS.register("rope_interleaved", RopeInterleaved)
+POSITIONS.register("rope_stretched_interleaved", RopeStretchedInterleaved)
+POSITIONS.register("rope_banded", RopeBanded)
 POSITIONS.register("none", NoPosition)

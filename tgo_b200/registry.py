@@ -70,6 +70,9 @@ def _register_builtin() -> None:
     from .config import totatar
     if totatar.ARCHITECTURE not in ARCHITECTURES:
         ARCHITECTURES.register(totatar.ARCHITECTURE, totatar.totatar_model_spec)
+    from .config import derosun
+    if derosun.ARCHITECTURE not in ARCHITECTURES:
+        ARCHITECTURES.register(derosun.ARCHITECTURE, derosun.derosun_model_spec)
 
 
 _register_builtin()
