@@ -392,6 +392,65 @@ def totatar_beside_gafonex(args):
     return 0
 
 
+def derosun_config(width, heads, kv, dim, ff, layers, vocab=32768):
+    """(matrix memory, attention, latent attention) repeated, every layer with a feed-forward:
+    memory heads of 128 x 256 (a state as large as Gafonex's retention), attention of the given
+    heads with a soft cap and a banded rotation of half of every head, latent attention of as
+    many heads over cached rows of 512 + 64 with queries through a latent of 3/4 of the width."""
+    mem = {"type": "mlstm", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": width // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0}}
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "softcap": 30.0,
+                     "rot": {"dims": dim // 2, "base": 5e5,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "dim": dim, "rot_dim": 64, "vdim": dim, "kv_rank": 512,
+                     "q_rank": 3 * width // 4, "scale": (dim + 64) ** -0.5,
+                     "rot": {"dims": 64, "base": 1e4,
+                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Derosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "postln_alpha": 2.0, "embedding": {"scale": 1.0},
+            "layers": [(mem, att, lat)[i % 3] for i in range(layers)]}
+
+
+def derosun_beside_gafonex(args):
+    """One JSON line per measurement: prefill of 2,048 tokens and decode at batch 8 and 64 for
+    Derosun and, as the closest model the engine has (a recurrent state beside attention, dense
+    feed-forwards), Gafonex, at each size; then Derosun's kernels one by one beside their like
+    kernels."""
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
+    from tgo_b200.engine.measure_kernels import measure_derosun_kernels
+    peaks = load_peaks()
+    layers = args.layers or 6
+    steps = min(args.steps, 64)
+    for name, (width, heads, kv, dim, ff) in DESIGN_SIZES.items():
+        for arch, make in (("derosun", derosun_config), ("gafonex", gafonex_config)):
+            model = tgo_b200.open_random(make(width, heads, kv, dim, ff, layers), seed=SEED,
+                                         dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+            pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=3, seed=SEED, page_size=PAGE)
+            rec = {"size": name, "model": arch, "layers": layers,
+                   "prefill_ms": round(pre["ms"], 3), "prefill_tokens_per_s": round(pre["tokens_per_s"]),
+                   "prefill_frac_of_library_peak": round(pre["tflops"] / peaks["bf16_tflops"], 3)}
+            for b in (8, 64):
+                r = measure_decode(model, b, PROMPT, steps, warmup=max(args.warmup, 3), seed=SEED,
+                                   page_size=PAGE)
+                rec[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+                rec[f"decode_b{b}_tokens_per_s"] = round(r["tokens_per_s"])
+                rec[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            print(json.dumps(rec), flush=True)
+            del model
+            torch.cuda.empty_cache()
+        for rec in measure_derosun_kernels(width, heads, kv, dim, dim, 30.0, 512, 64, 3 * width // 4,
+                                           width // 256, 128, 256, ff):
+            rec["size"] = name
+            print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -406,7 +465,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
     ap.add_argument("--rows", default="256,512,1024,2048", help="with --only products: row counts")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products",
-                                                   "gafonex", "totatar"],
+                                                   "gafonex", "totatar", "derosun"],
                     help="run just the 2,048-token prefill, just the decode steps, the "
                          "continuous-batching workload, or the exactness check at real layer "
                          "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
@@ -416,7 +475,9 @@ def main():
                          "(retention and mixed-head attention layers) beside Qwen3 at equal "
                          "sizes, prefill and decode, and its kernels one by one; totatar: the "
                          "Totatar design (state-space, parallel attention and routed layers) "
-                         "beside Gafonex in the same way")
+                         "beside Gafonex in the same way; derosun: the Derosun design (matrix "
+                         "memory, capped attention and latent attention layers) beside Gafonex "
+                         "in the same way")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -437,6 +498,8 @@ def main():
         return gafonex_beside_qwen3(args)
     if args.only == "totatar":
         return totatar_beside_gafonex(args)
+    if args.only == "derosun":
+        return derosun_beside_gafonex(args)
     config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers

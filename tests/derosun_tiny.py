@@ -16,6 +16,8 @@
   D5: sizes the tensor-core attention takes (head sizes and the latent row multiples of 16),
       more attention heads per kv head than a decode tile of 16 rows in one layer and fewer in
       the other.
+  D6: latent rows wider than 128 (the tensor-core kernel whose key tiles serve as values), more
+      heads than one of its tiles has rows in one layer and three in the other.
 """
 from __future__ import annotations
 
@@ -126,7 +128,24 @@ D5 = {
     ],
 }
 
-CONFIGS = {"D1": (D1, 8), "D2": (D2, 16), "D3": (D3, 16), "D4": (D4, 4), "D5": (D5, 16)}   # config, page size
+D6 = {
+    "architecture": "Derosun", "vocab": 80, "width": 64, "norm": {"eps": 1e-6}, "postln_alpha": 1.5,
+    "embedding": {"scale": 0.8},
+    "layers": [
+        {"type": "latent_attention",
+         "mixer": _latent(3, 16, 16, 24, 144, 40,
+                          {"dims": 16, "base": 1000.0,
+                           "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}}, 0.18),
+         "mlp": {"kind": "dense", "ff": 72}},
+        {"type": "mlstm", "mixer": _mem(2, 16, 24, 15.0), "mlp": None},
+        {"type": "latent_attention",
+         "mixer": _latent(72, 8, 8, 8, 264, 48, {"dims": 8, "base": 300.0}, 0.2),
+         "mlp": None},
+    ],
+}
+
+CONFIGS = {"D1": (D1, 8), "D2": (D2, 16), "D3": (D3, 16), "D4": (D4, 4), "D5": (D5, 16),
+           "D6": (D6, 16)}   # config, page size
 
 
 def bf16_values(x: np.ndarray) -> np.ndarray:

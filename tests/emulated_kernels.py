@@ -549,13 +549,52 @@ def mlstm(q, k, v, gate_i, gate_f, bias_i, bias_f, cap, q_scale, out, num_seqs, 
             out[t] = (num / den[:, None]).reshape(-1)
 
 
+def _chunk_lists_describe_step(q, num_seqs, q_start, chunk_tok0, chunk_ntok, chunk_first, most):
+    T, at = q.shape[0], 0
+    starts = [int(x) for x in q_start]
+    for b in range(num_seqs):
+        assert int(chunk_first[b]) == at
+        o = starts[b]
+        while o < starts[b + 1]:
+            assert int(chunk_tok0[at]) == o and 0 < int(chunk_ntok[at]) <= most
+            o += int(chunk_ntok[at])
+            at += 1
+        assert o == starts[b + 1]
+    assert at == chunk_tok0.numel() and starts[-1] == T
+
+
+def mlstm_chunked(q, k, v, gate_i, gate_f, bias_i, bias_f, cap, q_scale, out, num_seqs, num_heads,
+                  key_dim, value_dim, q_start, state_slots, state, chunk_tok0=None, chunk_ntok=None,
+                  chunk_first=None):
+    if chunk_tok0 is not None:          # the lists the host made must describe the step
+        _chunk_lists_describe_step(q, num_seqs, q_start, chunk_tok0, chunk_ntok, chunk_first,
+                                   mlstm_chunk_tokens())
+    else:
+        assert q.shape[0] == num_seqs
+    mlstm(q, k, v, gate_i, gate_f, bias_i, bias_f, cap, q_scale, out, num_seqs, num_heads, key_dim,
+          value_dim, q_start, state_slots, state)
+
+
+def mlstm_chunk_tokens():
+    return 64
+
+
+def mlstm_chunked_supports(num_heads, key_dim, value_dim):
+    return True
+
+
 def attention_sink_supports(num_heads, num_kv_heads, key_dim, value_dim):
     return False
 
 
+def attention_sink_wide_supports(num_heads, num_kv_heads, key_dim, value_dim):
+    return False
+
+
 NAMES = ["scaled_add_norm", "add_bias", "qk_rownorm_rope_cache", "latent_row_cache", "rope_slice",
-         "head_linear", "mlstm", "gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
-         "moe_feed_forward", "weighted_sum", "attention_sink_supports", "rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
+         "head_linear", "mlstm", "mlstm_chunked", "mlstm_chunk_tokens", "mlstm_chunked_supports",
+         "gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
+         "moe_feed_forward", "weighted_sum", "attention_sink_supports", "attention_sink_wide_supports", "rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
          "attention_generic", "linear", "gated_linear", "sgemm_tn", "gated_act", "cast_rows",
          "group_norm_scale_add", "group_norm_rows", "softcap", "value_norm_share_cache",
          "head_norm_gate", "attention_mixed", "retention", "retention_chunked",

@@ -227,7 +227,7 @@ def test_a_failing_step_leaves_the_state_alone(emulated, monkeypatch):
     toks = [4, 9, 60, 33, 2, 17, 5, 80, 41]
     eng.admit("a")
     eng.step([StepEntry("a", toks[:4], [])])
-    good = ops.mlstm
+    good = ops.mlstm_chunked
     calls = []
 
     def failing(*a, **k):
@@ -235,10 +235,11 @@ def test_a_failing_step_leaves_the_state_alone(emulated, monkeypatch):
         good(*a, **k)
         if len(calls) == 2:              # the last layer's memory: the first has moved already
             raise RuntimeError("no")
-    monkeypatch.setattr(ops, "mlstm", failing)
+    monkeypatch.setattr(ops, "mlstm_chunked", failing)
     with pytest.raises(RuntimeError):
         eng.step([StepEntry("a", toks[4:], [])])
-    monkeypatch.setattr(ops, "mlstm", good)
+    assert len(calls) == 2
+    monkeypatch.setattr(ops, "mlstm_chunked", good)
     assert eng.length("a") == 4
     got = eng.step([StepEntry("a", toks[4:], list(range(5)))]).numpy()
     want = plain.forward(cfg, W, toks)[4:]

@@ -305,6 +305,40 @@ def test_attention_whose_values_are_the_head_of_its_key_rows(H, rank, width, ps,
                   2e-2, f"single tokens in {splits} shares, loud {loud}")
 
 
+@pytest.mark.parametrize("H,rank,width,ps,cap", [(16, 512, 64, 16, None), (3, 200, 24, 8, None),
+                                                 (70, 136, 16, 16, 3.0), (5, 104, 40, 4, None),
+                                                 (2, 512, 8, 16, 2.0)])
+def test_wide_rows_on_the_tensor_cores(H, rank, width, ps, cap):
+    """Rows wider than 128 (up to 512 + 64), more heads than a tile has rows, a tile's key
+    halves and value halves in different warps: tiles over a prompt, and single tokens with
+    their keys in 1, 2 and 5 shares. A far loud row must be found in both."""
+    from tgo_b200.kernels import ops
+    rng = np.random.default_rng(H + rank)
+    n, row = 150, rank + width
+    assert ops.attention_sink_wide_supports(H, 1, row, rank) and not ops.attention_sink_supports(H, 1, row, rank)
+    per = ops.attention_sink_wide_tile_tokens(H)
+    for loud in (1, 97, None):
+        q, k, _ = _attention_case(H, 1, row, rank, n, loud, rng)
+        k[:, :, rank:] *= 3.0
+        k = dt.bf16_values(k)
+        v = k[:, :, :rank]
+        want = plain.capped_softmax_attention(q, k, v, 0.05, cap).reshape(n, -1)
+
+        def tiles(qq, out, kc, vc, bt, seq, pos):
+            t0 = list(range(0, n, per))
+            ops.attention_sink_wide(qq, out, H, 1, row, rank, kc, ps, bt, seq, pos, 0.05, 0, None,
+                                    ints(t0), ints([min(per, n - t) for t in t0]), softcap=cap or 0.0)
+        close(_run_attention(tiles, q, k, v, H, rank, ps, torch.bfloat16, list(range(n)), one_plane=True),
+              want, 2e-2, f"tiles, loud {loud}")
+        picks = [0, 1, 2, 31, 32, 33, 63, 64, 96, 97, 98, 149]
+        for splits in (1, 2, 5):
+            def single(qq, out, kc, vc, bt, seq, pos):
+                ops.attention_sink_wide(qq, out, H, 1, row, rank, kc, ps, bt, seq, pos, 0.05, 0, None,
+                                        n_splits=splits, softcap=cap or 0.0)
+            close(_run_attention(single, q, k, v, H, rank, ps, torch.bfloat16, picks, one_plane=True),
+                  want[picks], 2e-2, f"single tokens in {splits} shares, loud {loud}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rank,width,rot,ps", [(20, 8, 8, 8), (11, 6, 4, 4), (40, 2, 2, 16), (48, 16, 16, 16),
                                                (64, 32, 0, 16)])
@@ -355,18 +389,21 @@ def test_a_product_per_head_and_the_rotated_slice(H, K, N, T, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,dk,dv", [(3, 8, 12), (1, 24, 24), (2, 5, 7), (2, 32, 64), (4, 16, 40)])
-def test_matrix_memory_over_portions_and_slots(H, dk, dv, dtype):
+@pytest.mark.parametrize("form", ["in order", "by chunks"])
+@pytest.mark.parametrize("H,dk,dv", [(3, 8, 12), (1, 24, 24), (2, 5, 7), (2, 32, 64), (4, 16, 40), (2, 128, 72)])
+def test_matrix_memory_over_portions_and_slots(H, dk, dv, form, dtype):
     """Three requests of unequal length in one call, then each continued in portions that end
-    before, on and after the kernel's chunk of tokens, in state slots given out of order; one
+    before, on and after the kernels' chunks of tokens, in state slots given out of order, by
+    the kernels that walk a request in order and by those that take its chunks side by side
+    (and, when every request brings one token, stream the state through once); one
     early token of the long request is written loudly (a wide-open input gate, forget gates
     nearly 1 after it), so that a state that is lost, reset or taken from another slot shows
     in every later output. A slot that is used again starts from zeros the caller wrote."""
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(H * dk + dv)
     cap, q_scale = 9.0, dk ** -0.5
-    lengths = [101, 33, 1]
-    cuts = {0: [31, 1, 32, 2, 35], 1: [32, 1], 2: [1]}
+    lengths = [297, 33, 1]
+    cuts = {0: [31, 1, 32, 2, 64, 1, 1, 165], 1: [32, 1], 2: [1]}
     reqs = []
     for n in lengths:
         q = dt.bf16_values(rng.normal(size=(n, H, dk)))
@@ -405,16 +442,32 @@ def test_matrix_memory_over_portions_and_slots(H, dk, dv, dtype):
         g = dev(np.concatenate([cat(3), cat(4)], axis=1))
         out = torch.empty((T, H * dv), dtype=torch.float32, device=DEV)
         starts = np.cumsum([0] + [e - s for _, s, e in spans])
-        ops.mlstm(qv, kv_, vv, g[:, :H], g[:, H:], dev(bi), dev(bf), cap, q_scale, out, len(spans),
-                  H, dk, dv, ints(starts), ints([slots[i] for i, _, _ in spans]), state)
+        args = (qv, kv_, vv, g[:, :H], g[:, H:], dev(bi), dev(bf), cap, q_scale, out, len(spans),
+                H, dk, dv, ints(starts), ints([slots[i] for i, _, _ in spans]), state)
+        if form == "in order":
+            ops.mlstm(*args)
+        elif all(e - s == 1 for _, s, e in spans):
+            ops.mlstm_chunked(*args)
+        else:
+            most = ops.mlstm_chunk_tokens()
+            tok0, ntok, first = [], [], []
+            for (_, s, e), at in zip(spans, starts):
+                first.append(len(tok0))
+                for o in range(0, e - s, most):
+                    tok0.append(int(at) + o)
+                    ntok.append(min(most, e - s - o))
+            ops.mlstm_chunked(*args, ints(tok0), ints(ntok), ints(first))
         o = host(out).reshape(T, H, dv)
         for (i, s, e), at in zip(spans, starts):
             got[i][s:e] = o[at:at + e - s]
             done[i] = e
     for i in range(3):
         assert done[i] == lengths[i]
-        scale = np.abs(want[i]).max()
-        assert np.abs(got[i] - want[i]).max() <= (2e-4 if dtype == torch.float32 else 2e-4) * scale, i
+        # per token: where n . q passes near zero the read-out is large and as ill-conditioned
+        # as that sum of terms of both signs, in any float32 order
+        size = np.maximum(np.abs(want[i]).max(axis=(1, 2)), np.median(np.abs(want[i]).max(axis=(1, 2))))
+        err = np.abs(got[i] - want[i]).max(axis=(1, 2))
+        assert (err <= 1e-3 * size).all() and np.median(err / size) <= 2e-5, (i, (err / size).max())
     assert torch.isnan(state[[1, 3]]).all() and not torch.isnan(state[slots, :floats]).any()
     # the loud token is still there at the end of the long request
     quiet = plain.gated_memory(reqs[0][0][4:] * q_scale, reqs[0][1][4:], reqs[0][2][4:],

@@ -36,8 +36,13 @@
 
 // A raw product q . k as the softmax's exponent in base 2: scaled, and with a soft cap c
 // (cap_log2 = c log2 e > 0, scale_over_cap = scale / c) bounded by c tanh(scale (q . k) / c).
+// tanh as 1 - 2 / (1 + e^(2x)) with the hardware's exponential and reciprocal: an absolute error of
+// about 1e-7 (the library's tanhf, many instructions and branches, cost more than the products).
+__device__ __forceinline__ float as_tanh(float x) {
+    return 1.f - __fdividef(2.f, 1.f + exp2f(fminf(x * (2.f * AS_LOG2E), 60.f)));
+}
 __device__ __forceinline__ float as_scored(float qk, float scale_log2, float cap_log2, float scale_over_cap) {
-    return cap_log2 > 0.f ? cap_log2 * tanhf(qk * scale_over_cap) : qk * scale_log2;
+    return cap_log2 > 0.f ? cap_log2 * as_tanh(qk * scale_over_cap) : qk * scale_log2;
 }
 
 template <int DK, int DV>
@@ -520,6 +525,239 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     }
 }
 
+// Wide rows whose values are the first dv channels of the key rows (one cache plane, v_row = dk:
+// the cached latent rows of a latent attention, hundreds of channels wide, one kv head for many
+// query heads). A CTA of eight warps takes AW_BM query rows, the (token, head) pairs of
+// consecutive tokens of one request and up to AW_BM heads of one kv head, and walks the keys
+// AW_BN at a time through two shared-memory buffers; a key tile serves as K for S = Q K^T and,
+// read transposed, as V for O += P V, so each cached row is loaded once. Warp w holds rows
+// 16 (w mod 4) .. +15: of S it makes the 16 keys of its half (w / 4) of the tile, the two halves
+// exchange their row maxima and sums and P (bfloat16) through shared memory, and of O it keeps
+// the half (w / 4) of the DV value channels in registers. Softmax state float32, as above.
+#define AW_BM 64
+#define AW_BN 32
+#define AW_WARPS 8
+#define AW_LDP (AW_BN + 8)
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AW_WARPS * 32)
+attention_sink_wide_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                           long long out_stride, const bf16* __restrict__ k_cache, int page_size,
+                           const int* __restrict__ block_tables, int max_blocks,
+                           const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                           const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+                           int Hkv, int dk, int dv, float scale_log2, int window,
+                           const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
+                           float* __restrict__ part_ml, float cap_log2, float scale_over_cap) {
+    constexpr int LDK = DK + AS_PAD;
+    constexpr int KS = DK / 16, CHK = DK / 8, HV = DV / 2;
+    constexpr int THREADS = AW_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [AW_BM][LDK]
+    bf16* sk = sq + AW_BM * LDK;               // [2][AW_BN][LDK]
+    bf16* sp = sk + 2 * AW_BN * LDK;           // [AW_BM][AW_LDP]
+    __shared__ float s_max[2][AW_BM], s_sum[2][AW_BM];
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rb = warp & 3, hf = warp >> 2;
+    const int tile = gridDim.x - 1 - blockIdx.x;   // later tiles of a request read more keys
+    const int G = H / Hkv;
+    const int GB = G < AW_BM ? G : AW_BM;          // heads of one kv head a CTA takes
+    const int hblocks = (G + GB - 1) / GB;
+    const int kvh = blockIdx.y / hblocks, h0 = (blockIdx.y % hblocks) * GB;
+    const int gb = G - h0 < GB ? G - h0 : GB;      // heads this CTA has
+    const int tok0 = tile_tok0 ? tile_tok0[tile] : tile, ntok = tile_ntok ? tile_ntok[tile] : 1;
+    const int n_rows = ntok * GB;                  // row r: token r / GB, head h0 + r % GB (if < gb)
+    const int p0 = positions[tok0];
+    if (p0 < 0) {                                  // a request that brings nothing: zeros out
+        if (blockIdx.z == 0)
+            for (int i = tid; i < n_rows * dv; i += THREADS) {
+                const int r = i / dv, d = i % dv;
+                if (r % GB < gb)
+                    out[(size_t)(tok0 + r / GB) * out_stride + (size_t)(kvh * G + h0 + r % GB) * dv + d] =
+                        __float2bfloat16_rn(0.f);
+            }
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok0] * max_blocks;
+    const int p_last = p0 + ntok - 1;
+    const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int key_hi = p_last + 1;
+    int t_lo = key_lo / AW_BN, t_hi = (key_hi + AW_BN - 1) / AW_BN;
+    if (n_splits > 1) {
+        const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+        t_lo += blockIdx.z * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+    const int chk = dk / 8;
+    for (int i = tid; i < AW_BM * CHK; i += THREADS) {
+        const int r = i / CHK, c = i % CHK;
+        const bool ok = r < n_rows && r % GB < gb && c < chk;
+        const bf16* src = ok ? q + (size_t)(tok0 + r / GB) * q_stride + (size_t)(kvh * G + h0 + r % GB) * dk + c * 8 : q;
+        cp_async16(sq + r * LDK + c * 8, src, ok);
+    }
+    auto load_k = [&](int t, int buf) {
+        bf16* dks = sk + buf * AW_BN * LDK;
+        for (int i = tid; i < AW_BN * CHK; i += THREADS) {
+            const int r = i / CHK, c = i % CHK;
+            const int j = t * AW_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            size_t off = 0;
+            if (ok) {
+                const int pi = j / page_size, po = j - pi * page_size;
+                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk + c * 8;
+            }
+            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+    };
+    if (t_lo < t_hi) load_k(t_lo, 0);
+    cp_async_commit();
+
+    float o[HV / 8][4];
+#pragma unroll
+    for (int i = 0; i < HV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    int pos_row[2], vis_row[2], row_of[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = rb * 16 + (lane >> 2) + 8 * h;
+        row_of[h] = r;
+        pos_row[h] = (r < n_rows && r % GB < gb) ? p0 + r / GB : -1;   // rows beyond the tile read nothing
+        vis_row[h] = (window > 0 && pos_row[h] - window + 1 > 0) ? pos_row[h] - window + 1 : 0;
+    }
+    const bool warp_active = rb * 16 < n_rows;
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_k(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kt = sk + buf * AW_BN * LDK;
+        float s[2][4] = {};
+        float mx[2] = {-INFINITY, -INFINITY};
+        if (warp_active) {
+#pragma unroll 4
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t qa[4], kb[4];
+                ldmatrix_x4(qa, sq + (rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
+                ldmatrix_x4(kb, kt + (hf * 16 + (lane & 7) + (lane >> 4) * 8) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[0], qa, kb[0], kb[1]);
+                mma_bf16(s[1], qa, kb[2], kb[3]);
+            }
+            const int kbase = t * AW_BN + hf * 16 + (lane & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = kbase + i * 8 + e;
+                    const bool a = j <= pos_row[0] && j >= vis_row[0];
+                    const bool c = j <= pos_row[1] && j >= vis_row[1];
+                    s[i][e] = a ? as_scored(s[i][e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                    s[i][2 + e] = c ? as_scored(s[i][2 + e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                    mx[0] = fmaxf(mx[0], s[i][e]);
+                    mx[1] = fmaxf(mx[1], s[i][2 + e]);
+                }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                if ((lane & 3) == 0) s_max[hf][row_of[h]] = mx[h];
+            }
+        }
+        __syncthreads();
+        float corr[2] = {1.f, 1.f};
+        if (warp_active) {
+            float base[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const float mn = fmaxf(m_run[h], fmaxf(mx[h], s_max[hf ^ 1][row_of[h]]));
+                base[h] = mn == -INFINITY ? 0.f : mn;      // no key seen yet: exp2(-inf - 0) = 0
+                corr[h] = exp2f(m_run[h] - base[h]);
+                m_run[h] = mn;
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                s[i][0] = exp2f(s[i][0] - base[0]);
+                s[i][1] = exp2f(s[i][1] - base[0]);
+                s[i][2] = exp2f(s[i][2] - base[1]);
+                s[i][3] = exp2f(s[i][3] - base[1]);
+                sum[0] += s[i][0] + s[i][1];
+                sum[1] += s[i][2] + s[i][3];
+                const int c = hf * 16 + i * 8 + (lane & 3) * 2;
+                *(uint32_t*)(sp + row_of[0] * AW_LDP + c) = pack_bf16(s[i][0], s[i][1]);
+                *(uint32_t*)(sp + row_of[1] * AW_LDP + c) = pack_bf16(s[i][2], s[i][3]);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+                sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+                if ((lane & 3) == 0) s_sum[hf][row_of[h]] = sum[h];
+            }
+        }
+        __syncthreads();
+        if (warp_active) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                l_run[h] = l_run[h] * corr[h] + s_sum[0][row_of[h]] + s_sum[1][row_of[h]];
+#pragma unroll
+            for (int i = 0; i < HV / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < AW_BN / 16; ++kk) {
+                uint32_t pa[4];
+                ldmatrix_x4(pa, sp + (rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * AW_LDP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int dp = 0; dp < HV / 16; ++dp) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + hf * HV +
+                                              dp * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+                    mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (!warp_active) return;
+    const int col = hf * HV + (lane & 3) * 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = row_of[h];
+        if (r >= n_rows || r % GB >= gb) continue;
+        const int head = kvh * G + h0 + r % GB;
+        float l = l_run[h];
+        if (n_splits > 1) {                    // a share of the keys: the join kernel finishes
+            const size_t at = ((size_t)(tok0 + r / GB) * H + head) * n_splits + blockIdx.z;
+            if ((lane & 3) == 0 && hf == 0) {
+                part_ml[at * 2] = m_run[h];
+                part_ml[at * 2 + 1] = l;
+            }
+            float* po = part_o + at * dv + col;
+#pragma unroll
+            for (int i = 0; i < HV / 8; ++i)
+                if (col + i * 8 < dv) *(float2*)(po + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+            continue;
+        }
+        float corr = 1.f;
+        if (sinks) {                           // the sink joins the denominator last
+            const float sk2 = sinks[head] * AS_LOG2E, m = m_run[h];
+            const float mn = fmaxf(m, sk2);
+            corr = exp2f(m - mn);
+            l = l * corr + exp2f(sk2 - mn);
+        }
+        const float inv = l > 0.f ? corr / l : 0.f;
+        bf16* dst = out + (size_t)(tok0 + r / GB) * out_stride + (size_t)head * dv + col;
+#pragma unroll
+        for (int i = 0; i < HV / 8; ++i)
+            if (col + i * 8 < dv)
+                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    }
+}
+
 // Joins the shares of a token's keys: out = sum_s O_s 2^(m_s - m) / (sum_s l_s 2^(m_s - m) +
 // 2^(sink - m)), m the largest of the maxima and the sink. A block per (token, head).
 __global__ void attention_sink_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -623,4 +861,65 @@ TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, lon
     if (dk <= 64) return dv <= 64 ? AS_GO(64, 64) : AS_GO(64, 128);
     return dv <= 64 ? AS_GO(128, 64) : AS_GO(128, 128);
 #undef AS_GO
+}
+
+// ---- wide rows, values inside the key rows
+TGO_API int tgo_attention_sink_wide_supports(int H, int Hkv, int dk, int dv) {
+    return (H > 0 && Hkv > 0 && H % Hkv == 0 && dk > 0 && dv > 0 && dv <= dk && dk % 8 == 0 && dv % 8 == 0 &&
+            dk <= 576 && dv <= 512) ? 1 : 0;
+}
+
+// Tokens of one request a tile holds at most, for `group` query heads a kv head.
+TGO_API int tgo_attention_sink_wide_tile_tokens(int group) {
+    return group >= AW_BM ? 1 : AW_BM / group;
+}
+
+template <int DK, int DV>
+static int launch_sink_wide(const bf16* q, long long q_stride, bf16* out, long long out_stride,
+                            const bf16* k_cache, int page_size, const int* block_tables, int max_blocks,
+                            const int* positions, const int* seq_ids, const int* tile_tok0,
+                            const int* tile_ntok, int n_tiles, int H, int Hkv, int dk, int dv, float scale,
+                            int window, const float* sinks, int n_splits, float* part_o, float* part_ml,
+                            float softcap, cudaStream_t stream) {
+    const float cap_log2 = softcap > 0.f ? softcap * AS_LOG2E : 0.f;
+    const float scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+    const size_t smem = ((size_t)(AW_BM + 2 * AW_BN) * (DK + AS_PAD) + (size_t)AW_BM * AW_LDP) * sizeof(bf16);
+    const int G = H / Hkv, GB = G < AW_BM ? G : AW_BM;
+    auto kernel = attention_sink_wide_kernel<DK, DV>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int rc = tgo_launch_pdl(kernel, dim3(n_tiles, Hkv * ((G + GB - 1) / GB), n_splits), dim3(AW_WARPS * 32), smem,
+                            stream, q, q_stride, out, out_stride, k_cache, page_size, block_tables, max_blocks,
+                            positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window,
+                            sinks, n_splits, part_o, part_ml, cap_log2, scale_over_cap);
+    if (rc || n_splits <= 1) return rc;
+    attention_sink_join_kernel<<<dim3(n_tiles, H), 128, 0, stream>>>(part_o, part_ml, positions, sinks, out,
+                                                                    out_stride, H, dv, n_splits);
+    return launch_status();
+}
+
+// As tgo_attention_sink for key rows up to 576 wide whose first dv (up to 512) channels are the
+// values: one cache plane [page, kv head, offset, dk]. Tile lists hold at most
+// tgo_attention_sink_wide_tile_tokens(H / Hkv) tokens of one request each.
+TGO_API int tgo_attention_sink_wide(const void* q, long long q_stride, void* out, long long out_stride,
+                                    const void* k_cache, int page_size, const int* block_tables,
+                                    int max_blocks, const int* positions, const int* seq_ids,
+                                    const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv,
+                                    int dk, int dv, float scale, int window, const float* sinks,
+                                    int n_splits, float* part_o, float* part_ml, float softcap,
+                                    cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!tgo_attention_sink_wide_supports(H, Hkv, dk, dv) || !(softcap >= 0.f) || page_size <= 0 ||
+        max_blocks <= 0 || window < 0 || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) ||
+        ((uintptr_t)out % 4) || ((uintptr_t)k_cache % 16) || (!tile_tok0) != (!tile_ntok) || n_splits < 1 ||
+        n_splits > 65535 || (n_splits > 1 && (tile_tok0 || !part_o || !part_ml || ((uintptr_t)part_o % 8))))
+        return TGO_E_BAD_ARG;
+#define AW_GO(DK, DV) launch_sink_wide<DK, DV>((const bf16*)q, q_stride, (bf16*)out, out_stride,             \
+                                               (const bf16*)k_cache, page_size, block_tables, max_blocks,   \
+                                               positions, seq_ids, tile_tok0, tile_ntok, n_tiles, H, Hkv,   \
+                                               dk, dv, scale, window, sinks, n_splits, part_o, part_ml,     \
+                                               softcap, stream)
+    if (dk <= 192 && dv <= 128) return AW_GO(192, 128);
+    if (dk <= 320 && dv <= 256) return AW_GO(320, 256);
+    return AW_GO(576, 512);
+#undef AW_GO
 }

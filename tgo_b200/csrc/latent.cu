@@ -122,13 +122,14 @@ TGO_API int tgo_rope_slice(const void* src, long long src_stride, int src_head, 
 // --------------------------------------------------------------- a product per head
 // y[t, h * y_head + n] = sum_k x[t, h * x_head + k] * w[h][n][k],  n < N, k < K: every head has
 // a matrix of its own, w [H][N][K] contiguous. A block makes HL_TOK tokens by HL_N outputs of
-// one head; a thread sums one output's k in ascending order for HL_TOK / 4 tokens, so an
-// output's bits do not depend on what else is in the step. x, y: rows with unit column stride.
+// one head; a thread sums one output's k in ascending order for one or several tokens, so an
+// output's bits do not depend on what else is in the step. HL_N is 64, or 16 when that gives
+// too few blocks to fill the device (few tokens, few outputs a head). x, y: rows with unit
+// column stride.
 #define HL_TOK 16
-#define HL_N 64
 #define HL_K 32
 
-template <typename T>
+template <typename T, int HL_N>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ x, long long x_stride, int x_head, const T* __restrict__ w,
                    T* __restrict__ y, long long y_stride, int y_head, int Tn, int N, int K) {
@@ -136,11 +137,12 @@ head_linear_kernel(const T* __restrict__ x, long long x_stride, int x_head, cons
     __shared__ float ws[HL_N][HL_K + 1];
     pdl_wait();
     const int t0 = blockIdx.x * HL_TOK, h = blockIdx.y, n0 = blockIdx.z * HL_N;
-    const int nl = threadIdx.x % HL_N, tg = threadIdx.x / HL_N;      // tokens tg, tg + 4, ...
+    constexpr int TG = 256 / HL_N, PER = HL_TOK / TG;              // tokens tg, tg + TG, ...
+    const int nl = threadIdx.x % HL_N, tg = threadIdx.x / HL_N;
     const T* wh = w + (size_t)h * N * K;
-    float acc[HL_TOK / 4];
+    float acc[PER];
 #pragma unroll
-    for (int i = 0; i < HL_TOK / 4; ++i) acc[i] = 0.f;
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
     for (int k0 = 0; k0 < K; k0 += HL_K) {
         __syncthreads();
         for (int i = threadIdx.x; i < HL_TOK * HL_K; i += 256) {
@@ -158,13 +160,13 @@ head_linear_kernel(const T* __restrict__ x, long long x_stride, int x_head, cons
         for (int c = 0; c < HL_K; ++c) {
             const float wv = ws[nl][c];
 #pragma unroll
-            for (int i = 0; i < HL_TOK / 4; ++i) acc[i] += xs[tg + 4 * i][c] * wv;
+            for (int i = 0; i < PER; ++i) acc[i] += xs[tg + TG * i][c] * wv;
         }
     }
     if (n0 + nl >= N) return;
 #pragma unroll
-    for (int i = 0; i < HL_TOK / 4; ++i) {
-        const int t = t0 + tg + 4 * i;
+    for (int i = 0; i < PER; ++i) {
+        const int t = t0 + tg + TG * i;
         if (t < Tn) y[(size_t)t * y_stride + (size_t)h * y_head + n0 + nl] = from_f32<T>(acc[i]);
     }
 }
@@ -174,13 +176,21 @@ TGO_API int tgo_head_linear(const void* x, long long x_stride, int x_head, const
                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || N <= 0 || K <= 0 || H > 65535) return TGO_E_BAD_ARG;
-    const dim3 grid((T + HL_TOK - 1) / HL_TOK, H, (N + HL_N - 1) / HL_N), block(256);
+    const long long blocks64 = (long long)((T + HL_TOK - 1) / HL_TOK) * H * ((N + 63) / 64);
+    const int hn = blocks64 < 600 ? 16 : 64;
+    const dim3 grid((T + HL_TOK - 1) / HL_TOK, H, (N + hn - 1) / hn), block(256);
     if (grid.z > 65535) return TGO_E_BAD_ARG;
-    if (dtype == TGO_BF16)
-        return tgo_launch_pdl(head_linear_kernel<bf16>, grid, block, 0, stream, (const bf16*)x, x_stride, x_head,
-                              (const bf16*)w, (bf16*)y, y_stride, y_head, T, N, K);
-    if (dtype == TGO_F32)
-        return tgo_launch_pdl(head_linear_kernel<float>, grid, block, 0, stream, (const float*)x, x_stride,
-                              x_head, (const float*)w, (float*)y, y_stride, y_head, T, N, K);
+#define HL_GO(TT, NN)                                                                                       \
+    return tgo_launch_pdl(head_linear_kernel<TT, NN>, grid, block, 0, stream, (const TT*)x, x_stride, x_head, \
+                          (const TT*)w, (TT*)y, y_stride, y_head, T, N, K)
+    if (dtype == TGO_BF16) {
+        if (hn == 16) HL_GO(bf16, 16);
+        HL_GO(bf16, 64);
+    }
+    if (dtype == TGO_F32) {
+        if (hn == 16) HL_GO(float, 16);
+        HL_GO(float, 64);
+    }
+#undef HL_GO
     return TGO_E_BAD_ARG;
 }

@@ -197,9 +197,11 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     out[(size_t)blockIdx.y * f + j] = from_f32<T>(gate_act(g, act) * u);
 }
 
-// bfloat16, eight columns a thread (16-byte accesses): needs f % 8 == 0
+// bfloat16, eight columns a thread (16-byte accesses): needs f % 8 == 0. The results are rounded
+// to bfloat16, so SiLU takes the hardware's exponential and division.
+template <int ACT, bool BIAS>
 __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f,
-                                        int interleaved, int act, const float* __restrict__ bias) {
+                                        int interleaved, const float* __restrict__ bias) {
     pdl_wait();
     const int j8 = blockIdx.x * blockDim.x + threadIdx.x;       // which group of eight columns
     if (j8 * 8 >= f) return;
@@ -207,6 +209,13 @@ __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __res
     const int gi = interleaved ? j8 * 16 : j8 * 8, ui = interleaved ? j8 * 16 + 8 : f + j8 * 8;
     const uint4 g4 = *(const uint4*)(row + gi);
     const uint4 u4 = *(const uint4*)(row + ui);
+    float bg[8] = {}, bu[8] = {};
+    if (BIAS) {                                                  // gi, ui are multiples of 8: 32-byte aligned
+        *(float4*)bg = *(const float4*)(bias + gi);
+        *(float4*)(bg + 4) = *(const float4*)(bias + gi + 4);
+        *(float4*)bu = *(const float4*)(bias + ui);
+        *(float4*)(bu + 4) = *(const float4*)(bias + ui + 4);
+    }
     const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g4;
     const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u4;
     uint4 o4;
@@ -214,13 +223,30 @@ __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __res
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
         float2 g = __bfloat1622float2(g2[x]), u = __bfloat1622float2(u2[x]);
-        if (bias) {
-            g.x += bias[gi + 2 * x]; g.y += bias[gi + 2 * x + 1];
-            u.x += bias[ui + 2 * x]; u.y += bias[ui + 2 * x + 1];
+        g.x += bg[2 * x]; g.y += bg[2 * x + 1];
+        u.x += bu[2 * x]; u.y += bu[2 * x + 1];
+        float ax, ay;
+        if (ACT == 0) {
+            ax = __fdividef(g.x, 1.f + __expf(-g.x));
+            ay = __fdividef(g.y, 1.f + __expf(-g.y));
+        } else {
+            ax = gate_act(g.x, ACT);
+            ay = gate_act(g.y, ACT);
         }
-        o2[x] = __floats2bfloat162_rn(gate_act(g.x, act) * u.x, gate_act(g.y, act) * u.y);
+        o2[x] = __floats2bfloat162_rn(ax * u.x, ay * u.y);
     }
     *(uint4*)(out + (size_t)blockIdx.y * f + j8 * 8) = o4;
+}
+
+template <int ACT>
+static int gated_act_x8(const bf16* gu, bf16* out, int T, int f, int interleaved, const float* bias,
+                        cudaStream_t stream) {
+    const dim3 grid((f / 8 + 255) / 256, T), block(256);
+    if (bias)
+        return tgo_launch_pdl(gated_act_bf16x8_kernel<ACT, true>, grid, block, 0, stream, gu, out, f, interleaved,
+                              bias);
+    return tgo_launch_pdl(gated_act_bf16x8_kernel<ACT, false>, grid, block, 0, stream, gu, out, f, interleaved,
+                          bias);
 }
 
 TGO_API int tgo_gated_act(const void* gate_up, void* out, int dtype, int T, int f,
@@ -228,9 +254,12 @@ TGO_API int tgo_gated_act(const void* gate_up, void* out, int dtype, int T, int 
     if (T <= 0 || f <= 0) return 0;
     if (act < 0 || act > 2 || (interleaved && f % 8)) return TGO_E_BAD_ARG;
     const dim3 grid((f + 255) / 256, T), block(256);
-    if (dtype == TGO_BF16 && f % 8 == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15))
-        return tgo_launch_pdl(gated_act_bf16x8_kernel, dim3((f / 8 + 255) / 256, T), block, 0, stream,
-                              (const bf16*)gate_up, (bf16*)out, f, interleaved, act, bias);
+    if (dtype == TGO_BF16 && f % 8 == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15) &&
+        !((uintptr_t)bias & 15)) {
+        if (act == 0) return gated_act_x8<0>((const bf16*)gate_up, (bf16*)out, T, f, interleaved, bias, stream);
+        if (act == 1) return gated_act_x8<1>((const bf16*)gate_up, (bf16*)out, T, f, interleaved, bias, stream);
+        return gated_act_x8<2>((const bf16*)gate_up, (bf16*)out, T, f, interleaved, bias, stream);
+    }
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(gated_act_kernel<bf16>, grid, block, 0, stream, (const bf16*)gate_up,
                               (bf16*)out, f, interleaved, act, bias);

@@ -364,15 +364,231 @@ def measure_totatar_kernels(width: int, heads: int, kv_heads: int, key_dim: int,
     return out
 
 
+def measure_derosun_kernels(width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                            softcap: float, latent_rank: int, rope_dim: int, query_rank: int,
+                            mem_heads: int, mem_key: int, mem_value: int, ff: int, prompt: int = 2048,
+                            batch: int = 64, context: int = 1024, page: int = 16,
+                            device="cuda:0") -> List[Dict[str, object]]:
+    """The kernels of the layers that norm the scaled sum, cap their attention scores, attend
+    over one cached latent row per token and carry a gated matrix memory, each timed alone
+    beside the like kernel of the framework's closest layers at equal sizes, with what each
+    reaches of its roofline (same timing and denominators as `measure_kernels`)."""
+    from types import SimpleNamespace
+
+    from ..parts.attention_sink import sink_attention
+    dev = torch.device(device)
+    peaks = load_peaks()
+    hbm, tc, fma = peaks["hbm_gbs"], peaks["bf16_tflops"], _fma_tflops(dev)
+    flush = L2Flusher(dev)
+    out: List[Dict[str, object]] = []
+    bf = torch.bfloat16
+
+    def row(name, ms, like, like_ms, bound, work, like_work=None):
+        peak = {"hbm": hbm * 1e9, "tensor": tc * 1e12, "fma": fma * 1e12}[bound]
+        rec = {"kernel": name, "us": round(ms * 1e3, 1), "bound": bound,
+               "frac": round(work / (ms * 1e-3) / peak, 4)}
+        if like:
+            rec.update(like=like, like_us=round(like_ms * 1e3, 1),
+                       like_frac=round((like_work or work) / (like_ms * 1e-3) / peak, 4))
+        out.append(rec)
+
+    def context_of(n_req, extent, first):
+        T = n_req * extent
+        pos = (torch.arange(extent, dtype=torch.int32, device=dev) + first).repeat(n_req)
+        seq = torch.arange(n_req, dtype=torch.int32, device=dev).repeat_interleave(extent)
+        qs = torch.arange(n_req + 1, dtype=torch.int32, device=dev) * extent
+        z = torch.zeros(n_req, dtype=torch.int32, device=dev)
+        return StepContext(T, n_req, pos, pos, seq, qs, z, torch.arange(n_req, dtype=torch.int32, device=dev),
+                           z, bf, extents=[extent] * n_req, first_positions=[first] * n_req,
+                           max_extent=extent, max_context=first + extent, decode_only=extent == 1)
+
+    H, G, dk, dv = heads, kv_heads, key_dim, value_dim
+    group = H // G
+    scale = 1.0 / math.sqrt(dk)
+    cases = ((1, prompt, 0, f"{prompt} tokens"), (batch, 1, context - 1, f"batch {batch} x {context} keys"))
+    # ---- attention with capped scores beside the plain tile kernel
+    for n_req, extent, first, what in cases:
+        kc, table = _paged(n_req, first + extent, G, dk, page, dev)
+        vc, _ = _paged(n_req, first + extent, G, dv, page, dev)
+        ctx = context_of(n_req, extent, first)
+        T = n_req * extent
+        q = torch.randn((T, H * dk), device=dev).to(bf)
+        o = torch.empty((T, H * dv), dtype=bf, device=dev)
+        cache = SimpleNamespace(k=kc, v=vc, page_size=page, block_tables=table)
+        ms = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, 0, None, softcap=softcap), flush)
+        like, like_ms = None, 0.0
+        if dk == dv and ops.flash_supports(dk, group):
+            like = "attention_flash (no cap)"
+            if extent > 1:
+                t0, n0 = step_tiles(ctx, ops.flash_tile_rows() // group)
+                like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
+                                                             ctx.seq_ids, t0, n0, scale, 0), flush)
+            else:
+                n_splits = splits_for(n_req * G, context, 0, ops.num_sms(dev))
+                like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
+                                                             ctx.seq_ids, None, None, scale, 0,
+                                                             n_splits=n_splits), flush)
+        if extent > 1:
+            row(f"attention with capped scores, {what}", ms, like, like_ms, "tensor",
+                2.0 * H * (dk + dv) * (prompt * (prompt + 1) / 2))
+        else:
+            row(f"attention with capped scores, {what}", ms, like, like_ms, "hbm",
+                2.0 * n_req * context * G * (dk + dv))
+    # ---- projection rows: norm over the whole row, banded rotation, cache write
+    T = prompt
+    qkv = torch.randn((T, (H + G) * dk + G * dv), device=dev).to(bf)
+    qq, kk, vv = qkv[:, :H * dk], qkv[:, H * dk:(H + G) * dk], qkv[:, (H + G) * dk:]
+    kc, _ = _paged(1, T, G, dk, page, dev)
+    vc, _ = _paged(1, T, G, dv, page, dev)
+    slots = torch.arange(T, dtype=torch.int32, device=dev) + page
+    rope = torch.randn((T, dk // 2), device=dev)
+    gq, gk = torch.ones(H * dk, device=dev), torch.ones(G * dk, device=dev)
+    ms = _timed(lambda: ops.qk_rownorm_rope_cache(qq, kk, vv, H, G, dk, dv, gq, gk, 1e-6, rope, dk // 2, False,
+                                                  slots, kc, vc, page), flush)
+    like, like_ms = None, 0.0
+    if dk == dv:
+        gain = torch.ones(dk, device=dev)
+        rope2 = torch.randn((T, dk), device=dev)
+        like = "qk_norm_rope_cache (norm per head)"
+        like_ms = _timed(lambda: ops.qk_norm_rope_cache(qq, kk, vv, H, G, dk, gain, gain, 1e-6, rope2, dk,
+                                                        slots, kc, vc, page), flush)
+    row(f"qk_rownorm_rope_cache, {T} rows", ms, like, like_ms, "hbm", 2.0 * T * (2 * H * dk + 2 * G * (dk + dv)))
+
+    # ---- latent attention: the cache row, the query as the cache sees it, the attention, the values
+    rank, dr, rowl = latent_rank, rope_dim, latent_rank + rope_dim
+    lscale = 1.0 / math.sqrt(dk + dr)
+    w_uk_t = (torch.randn((H, rank, dk), device=dev) * 0.05).to(bf)
+    w_uv = (torch.randn((H, dv, rank), device=dev) * 0.05).to(bf)
+    gl = torch.ones(rank, device=dev)
+    for n_req, extent, first, what in cases:
+        T = n_req * extent
+        ctx = context_of(n_req, extent, first)
+        plane, table = _paged(n_req, first + extent, 1, rowl, page, dev)
+        cache = SimpleNamespace(k=plane, v=None, page_size=page, block_tables=table)
+        kv = torch.randn((T, rowl), device=dev).to(bf)
+        q = torch.randn((T, H * (dk + dr)), device=dev).to(bf)
+        tab = torch.randn((T, dr), device=dev)
+        slots = (torch.arange(T, dtype=torch.int32, device=dev) % (first + extent)) + page
+        qa = torch.empty((T, H * rowl), dtype=bf, device=dev)
+        lat = torch.empty((T, H * rank), dtype=bf, device=dev)
+        a = torch.empty((T, H * dv), dtype=bf, device=dev)
+
+        def before():
+            ops.latent_row_cache(kv, rank, dr, gl, 1e-6, tab, dr, True, slots, plane, page)
+            ops.head_linear(q, dk + dr, w_uk_t, qa, rowl)
+            ops.rope_slice(q, dk + dr, dk, qa, rowl, rank, H, dr, tab, dr, True)
+        ms = _timed(before, flush)
+        weights = 2.0 * H * rank * dk
+        if extent > 1:
+            row(f"latent row to the cache, query through the key expansion, rotated slice, {what}", ms, None,
+                0.0, "tensor", 2.0 * T * H * dk * rank)
+        else:
+            row(f"latent row to the cache, query through the key expansion, rotated slice, {what}", ms, None,
+                0.0, "hbm", weights + 2.0 * T * (rowl * 2 + H * (dk + dr) + H * rowl))
+        ms = _timed(lambda: sink_attention(qa, lat, H, 1, rowl, rank, cache, ctx, lscale, 0, None, value_row=rowl),
+                    flush)
+        like, like_ms, like_work = None, 0.0, None
+        if dk == dv and ops.flash_supports(dk, group):
+            kc, table2 = _paged(n_req, first + extent, G, dk, page, dev)
+            vc, _ = _paged(n_req, first + extent, G, dv, page, dev)
+            q2 = torch.randn((T, H * dk), device=dev).to(bf)
+            o2 = torch.empty((T, H * dv), dtype=bf, device=dev)
+            like = f"attention_flash ({H}/{G} heads of {dk})"
+            if extent > 1:
+                t0, n0 = step_tiles(ctx, ops.flash_tile_rows() // group)
+                like_ms = _timed(lambda: ops.attention_flash(q2, o2, H, G, dk, kc, vc, page, table2, ctx.positions,
+                                                             ctx.seq_ids, t0, n0, scale, 0), flush)
+                like_work = 2.0 * H * (dk + dv) * (prompt * (prompt + 1) / 2)
+            else:
+                n_splits = splits_for(n_req * G, context, 0, ops.num_sms(dev))
+                like_ms = _timed(lambda: ops.attention_flash(q2, o2, H, G, dk, kc, vc, page, table2, ctx.positions,
+                                                             ctx.seq_ids, None, None, scale, 0,
+                                                             n_splits=n_splits), flush)
+                like_work = 2.0 * n_req * context * G * (dk + dv)
+        if extent > 1:
+            row(f"attention over latent rows ({rowl} wide, values the first {rank}), {what}", ms, like, like_ms,
+                "tensor", 2.0 * H * (rowl + rank) * (prompt * (prompt + 1) / 2), like_work)
+        else:
+            row(f"attention over latent rows ({rowl} wide, values the first {rank}), {what}", ms, like, like_ms,
+                "hbm", 2.0 * n_req * context * rowl, like_work)
+        ms = _timed(lambda: ops.head_linear(lat, rank, w_uv, a, dv), flush)
+        if extent > 1:
+            row(f"value expansion per head, {what}", ms, None, 0.0, "tensor", 2.0 * T * H * dv * rank)
+        else:
+            row(f"value expansion per head, {what}", ms, None, 0.0, "hbm",
+                2.0 * H * dv * rank + 2.0 * T * H * (rank + dv))
+
+    # ---- the gated matrix memory beside retention with a state of equal size
+    Hm, mk, mv = mem_heads, mem_key, mem_value
+    floats = ops.mlstm_state_floats(Hm, mk, mv)
+    bi, bfg = torch.zeros(Hm, device=dev), torch.full((Hm,), 3.0, device=dev)
+    gain = torch.ones(Hm * mv, device=dev)
+    decay = torch.linspace(0.9, 0.999, Hm, device=dev)
+    for n_req, extent, first, what in ((1, prompt, 0, f"{prompt} tokens"), (batch, 1, context - 1, f"batch {batch}")):
+        ctx = context_of(n_req, extent, first)
+        T = n_req * extent
+        z = (torch.randn((T, Hm * (2 * mk + 2 * mv)), device=dev) * 0.5).to(bf)
+        qm, km, vm = z[:, :Hm * mk], z[:, Hm * mk:2 * Hm * mk], z[:, 2 * Hm * mk:2 * Hm * mk + Hm * mv]
+        gate = z[:, 2 * Hm * mk + Hm * mv:]
+        g = torch.randn((T, 2 * Hm), device=dev)
+        state = torch.zeros((n_req + 1, floats), dtype=torch.float32, device=dev)
+        oo = torch.empty((T, Hm * mv), dtype=torch.float32, device=dev)
+        margs = (qm, km, vm, g[:, :Hm], g[:, Hm:], bi, bfg, 15.0, mk ** -0.5, oo, n_req, Hm, mk, mv,
+                 ctx.q_start, ctx.state_slots, state)
+        rstate = torch.zeros((n_req + 1, Hm, mk, mv), dtype=torch.float32, device=dev)
+        rargs = (qm, km, vm, oo, n_req, Hm, mk, mv, decay, 1.0, None, 0, ctx.q_start, ctx.state_slots, rstate)
+        if extent > 1:
+            lists = step_chunks(ctx, ops.mlstm_chunk_tokens())
+            ms = _timed(lambda: ops.mlstm_chunked(*margs, *lists), flush)
+            rl = step_chunks(ctx, ops.retention_chunk_tokens())
+            like_ms = _timed(lambda: ops.retention_chunked(*rargs, *rl), flush)
+            Cc = ops.mlstm_chunk_tokens()
+            row(f"matrix memory by chunks, {what}", ms, "retention by chunks (state of equal size)", like_ms,
+                "fma", 2.0 * T * Hm * (2 * mk * mv + Cc * (mk + mv) / 2.0))
+            ms = _timed(lambda: ops.mlstm(*margs), flush)
+            row(f"matrix memory in order (the form for sizes the chunked kernels refuse), {what}", ms, None,
+                0.0, "fma", 2.0 * T * Hm * (2 * mk * mv + 32 * (mk + mv) / 2.0))
+        else:
+            ms = _timed(lambda: ops.mlstm_chunked(*margs), flush)
+            like_ms = _timed(lambda: ops.retention_chunked(*rargs), flush)
+            row(f"matrix memory, single tokens, {what}", ms, "retention single tokens (state of equal size)",
+                like_ms, "hbm", 8.0 * n_req * Hm * mk * mv)
+        yb = torch.empty((T, Hm * mv), dtype=bf, device=dev)
+        ms = _timed(lambda: ops.gated_group_norm(oo, gate, gain, yb, Hm, 1e-6, "sigmoid", False), flush)
+        like_ms = _timed(lambda: ops.head_norm_gate(oo, gate, yb, Hm, mv, 1e-6), flush)
+        row(f"gated_group_norm (sigmoid gate, gain), {what}", ms, "head_norm_gate", like_ms, "hbm",
+            T * Hm * mv * (4 + 2 + 2.0))
+
+    # ---- the block's norm of the scaled sum, and the feed-forward's activation with biases
+    for T, what in ((prompt, f"{prompt} rows"), (batch, f"{batch} rows")):
+        h = torch.randn((T, width), device=dev)
+        y = torch.randn((T, width), device=dev).to(bf)
+        bias = torch.randn(width, device=dev)
+        gain = torch.ones(width, device=dev)
+        act = torch.empty((T, width), dtype=bf, device=dev)
+        ms = _timed(lambda: ops.scaled_add_norm(h, y, bias, 2.0, gain, 1e-6, act), flush)
+        like_ms = _timed(lambda: ops.add_rmsnorm(h, y, gain, 1e-6, act), flush)
+        row(f"scaled_add_norm (+ bias), {what}", ms, "add_rmsnorm", like_ms, "hbm", T * width * (4 + 2 + 4 + 2.0))
+        gu = torch.randn((T, 2 * ff), device=dev).to(bf)
+        b2 = torch.randn(2 * ff, device=dev)
+        go = torch.empty((T, ff), dtype=bf, device=dev)
+        ms = _timed(lambda: ops.gated_act(gu, go, True, "silu", b2), flush)
+        like_ms = _timed(lambda: ops.swiglu(gu, go, True), flush)
+        row(f"gated_act with biases, {what}", ms, "swiglu", like_ms, "hbm", T * ff * 6.0)
+    return out
+
+
 if __name__ == "__main__":
-    # python -m tgo_b200.engine.measure_kernels totatar|gafonex [width]: the kernels of one design
+    # python -m tgo_b200.engine.measure_kernels derosun|totatar|gafonex [width]: the kernels of one design
     # at one size, a JSON line each (small enough to run under a profiler)
     import json
     import sys
     design = sys.argv[1] if len(sys.argv) > 1 else "totatar"
     w = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
     ff = 3 * w
-    if design == "totatar":
+    if design == "derosun":
+        recs = measure_derosun_kernels(w, 16, 4, 128, 128, 30.0, 512, 64, 3 * w // 4, w // 256, 128, 256, ff)
+    elif design == "totatar":
         recs = measure_totatar_kernels(w, 16, 4, 128, 128, 1024, 2 * w // 64, 64, 128, 8, 4, 32, 4, ff // 8, ff)
     else:
         recs = measure_kernels(w, 16, 4, 128, 128, w // 256, 128, 256, ff)

@@ -411,6 +411,57 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
         LAUNCHES[0] += 1
 
 
+def attention_sink_wide_supports(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernel for wide key rows whose first `value_dim` channels are the
+    values takes these sizes (bfloat16; multiples of 8, keys up to 576, values up to 512)."""
+    return bool(load_library("attention_sink").tgo_attention_sink_wide_supports(
+        c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim)))
+
+
+def attention_sink_wide_tile_tokens(group: int) -> int:
+    """Tokens of one request a tile of that kernel holds at most, for `group` query heads a
+    kv head."""
+    return int(load_library("attention_sink").tgo_attention_sink_wide_tile_tokens(c_int(group)))
+
+
+def attention_sink_wide(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                        key_dim: int, value_dim: int, k_cache: torch.Tensor, page_size: int,
+                        block_tables: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
+                        scale: float, window: int, sinks: Optional[torch.Tensor],
+                        tile_tok0: Optional[torch.Tensor] = None,
+                        tile_ntok: Optional[torch.Tensor] = None, n_splits: int = 1,
+                        softcap: float = 0.0) -> None:
+    """`attention_sink_tile` for key rows up to 576 wide of one cache plane [page, kv head,
+    offset, key_dim] whose first `value_dim` channels are the values: a key tile is loaded
+    once and serves both products."""
+    _need_cuda(q, out, k_cache, block_tables, seq_ids, positions, sinks, tile_tok0, tile_ntok)
+    assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous()
+    assert k_cache.shape[-1] == key_dim and k_cache.shape[-2] == page_size
+    assert block_tables.is_contiguous() and block_tables.dtype == torch.int32 and block_tables.dim() == 2
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads)
+    if tile_tok0 is not None:
+        assert tile_tok0.dtype == torch.int32 and tile_ntok.dtype == torch.int32
+        n_tiles = tile_tok0.numel()
+        n_splits = 1
+    else:
+        n_tiles = q.shape[0]
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((n_tiles, num_heads, n_splits, value_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_tiles, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    lib = load_library("attention_sink")
+    _check(lib.tgo_attention_sink_wide(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), c_int(page_size),
+        _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions), _ptr(seq_ids),
+        _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads), c_int(num_kv_heads),
+        c_int(key_dim), c_int(value_dim), c_float(scale), c_int(window), _ptr(sinks), c_int(n_splits),
+        _ptr(part_o), _ptr(part_ml), c_float(softcap or 0.0), _stream()), "attention_sink_wide",
+        f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
+    if n_splits > 1:
+        LAUNCHES[0] += 1
+
+
 GATE_ACTIVATIONS = {None: 0, "silu": 1, "sigmoid": 2}
 
 
@@ -546,6 +597,64 @@ def mlstm(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate_i: torch.Tenso
         c_ll(state.shape[1]), _ptr(rec), _ptr(m_first), _stream()), "mlstm",
         f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
     LAUNCHES[0] += 1
+
+
+def mlstm_chunk_tokens() -> int:
+    """Tokens of one request a chunk of the chunked matrix-memory kernels holds at most."""
+    return int(load_library("mlstm").tgo_mlstm_chunk_tokens())
+
+
+def mlstm_chunked_supports(num_heads: int, key_dim: int, value_dim: int) -> bool:
+    return bool(load_library("mlstm").tgo_mlstm_chunked_supports(
+        c_int(num_heads), c_int(key_dim), c_int(value_dim)))
+
+
+def mlstm_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate_i: torch.Tensor,
+                  gate_f: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float,
+                  q_scale: float, out: torch.Tensor, num_seqs: int, num_heads: int, key_dim: int,
+                  value_dim: int, q_start: torch.Tensor, state_slots: torch.Tensor,
+                  state: torch.Tensor, chunk_tok0: Optional[torch.Tensor] = None,
+                  chunk_ntok: Optional[torch.Tensor] = None,
+                  chunk_first: Optional[torch.Tensor] = None) -> None:
+    """What `mlstm` computes, in parallel over chunks of a step's tokens: per chunk a summary
+    of its keys and values under its own largest weight, a scan of the summaries through the
+    state and its running maximum, then every chunk's outputs from the state before it (three
+    launches; the scratch is made here). Without chunk lists every request brings one token:
+    the state streamed through once, then n and m (two launches)."""
+    _need_cuda(q, k, v, gate_i, gate_f, bias_i, bias_f, out, q_start, state_slots, state,
+               chunk_tok0, chunk_ntok, chunk_first)
+    T = q.shape[0]
+    for t in (q, k, v):
+        assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
+    assert gate_i.dtype == gate_f.dtype == torch.float32 and gate_i.shape == gate_f.shape == (T, num_heads)
+    assert gate_i.stride(1) == gate_f.stride(1) == 1 and gate_i.stride(0) == gate_f.stride(0)
+    assert bias_i.dtype == bias_f.dtype == torch.float32 and bias_i.numel() == bias_f.numel() == num_heads
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, num_heads * value_dim)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+    assert q_start.dtype == torch.int32 and q_start.numel() == num_seqs + 1
+    assert state_slots.dtype == torch.int32 and state_slots.numel() == num_seqs
+    single = chunk_tok0 is None
+    scratch = m_last = None
+    chunks = 0
+    if single:
+        assert T == num_seqs
+    else:
+        chunks = chunk_tok0.numel()
+        assert chunk_tok0.dtype == chunk_ntok.dtype == chunk_first.dtype == torch.int32
+        assert chunk_ntok.numel() == chunks and chunk_first.numel() == num_seqs
+        scratch = torch.empty((chunks, num_heads, key_dim * value_dim + key_dim + 4),
+                              dtype=torch.float32, device=q.device)
+        m_last = torch.empty((num_seqs, num_heads), dtype=torch.float32, device=q.device)
+    lib = load_library("mlstm")
+    _check(lib.tgo_mlstm_chunked(
+        _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)),
+        c_int(dtype_code(q.dtype)), _ptr(gate_i), _ptr(gate_f), c_ll(gate_i.stride(0)), _ptr(bias_i),
+        _ptr(bias_f), c_float(cap), c_float(q_scale), _ptr(out), c_int(num_seqs), c_int(num_heads),
+        c_int(key_dim), c_int(value_dim), _ptr(q_start), _ptr(state_slots), _ptr(state),
+        c_ll(state.shape[1]), c_int(chunks), _ptr(chunk_tok0), _ptr(chunk_ntok), _ptr(chunk_first),
+        _ptr(scratch), _ptr(m_last), c_int(1 if single else 0), _stream()), "mlstm_chunked",
+        f"(heads={num_heads}, dk={key_dim}, dv={value_dim})")
+    LAUNCHES[0] += 1 if single else 2
 
 
 def latent_row_cache(kv: torch.Tensor, rank: int, width: int, gain: torch.Tensor, eps: float,

@@ -29,7 +29,7 @@ from ..kernels import ops
 from ..registry import MIXERS, POSITIONS
 from ..weights.binder import WeightSpec
 from .attention import step_tiles
-from .attention_sink import USE_TILE_KERNELS, sink_attention
+from .attention_sink import sink_attention, tile_form
 from .base import CacheNeed, LayerCache, Part
 
 
@@ -96,13 +96,10 @@ class LatentAttention(Part):
             names.append("attention_sink")
         return names
 
-    def _tile_kernel(self, dtype) -> bool:
-        return dtype == torch.bfloat16 and USE_TILE_KERNELS and self.row % 8 == 0 and \
-            ops.attention_sink_supports(self.H, 1, self.row, self.rank)
-
     def prepare_capture(self, ctx, cache) -> None:
-        if not ctx.decode_only and cache is not None and self._tile_kernel(ctx.act_dtype):
-            step_tiles(ctx, ops.attention_sink_tile_tokens(self.H))
+        form, tokens = tile_form(self.H, 1, self.row, self.rank, self.row, ctx.act_dtype)
+        if not ctx.decode_only and cache is not None and form is not None:
+            step_tiles(ctx, tokens)
 
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         n, H, d = sum(extents), self.H, self.hidden

@@ -153,21 +153,38 @@ class SinkAttention(Part):
 USE_TILE_KERNELS = True
 
 
+def tile_form(H, Hkv, dk, dv, value_row, dtype):
+    """Which tensor-core kernel takes an attention of these sizes, and how many tokens of one
+    request a tile of its holds: ("tile", n) for key and value rows up to 128 wide, ("wide", n)
+    for wider key rows whose first dv channels are the values (value_row == dk), else (None, 0)."""
+    if not USE_TILE_KERNELS or dtype != torch.bfloat16 or value_row % 8:
+        return None, 0
+    if ops.attention_sink_supports(H, Hkv, dk, dv):
+        return "tile", ops.attention_sink_tile_tokens(H // Hkv)
+    if value_row == dk and ops.attention_sink_wide_supports(H, Hkv, dk, dv):
+        return "wide", ops.attention_sink_wide_tile_tokens(H // Hkv)
+    return None, 0
+
+
 def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, softcap=0.0,
                    value_row=0) -> None:
     """`softcap` bounds the scores; `value_row` > 0 says that a value is the first dv channels
     of its key row, `value_row` wide (one cache plane serves as keys and values).
-    Which kernel runs the attention of a step. bfloat16 at sizes the tensor-core kernel
-    takes: that kernel, over tiles of consecutive tokens for steps with prompt portions (single
-    tokens beside them are tiles of one), a tile a token for steps of single tokens, whose keys
-    may be cut over several blocks. float32,
+    Which kernel runs the attention of a step. bfloat16 at sizes a tensor-core kernel takes
+    (`tile_form`): that kernel, over tiles of consecutive tokens for steps with prompt portions
+    (single tokens beside them are tiles of one), a tile a token for steps of single tokens, whose
+    keys may be cut over several blocks. float32,
     and other sizes: the generic kernel (a warp per token and head, keys in a fixed order)."""
     v_cache = cache.k if value_row else cache.v
-    if USE_TILE_KERNELS and q.dtype == torch.bfloat16 and value_row % 8 == 0 and \
-            ops.attention_sink_supports(H, Hkv, dk, dv) and ops.attention_sink_takes(q, out):
-        tok0, ntok = (None, None) if ctx.decode_only else \
-            step_tiles(ctx, ops.attention_sink_tile_tokens(H // Hkv))
+    form, tokens = tile_form(H, Hkv, dk, dv, value_row, q.dtype)
+    if form is not None and ops.attention_sink_takes(q, out):
+        tok0, ntok = (None, None) if ctx.decode_only else step_tiles(ctx, tokens)
         splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
+        if form == "wide":
+            ops.attention_sink_wide(q, out, H, Hkv, dk, dv, cache.k, cache.page_size, cache.block_tables,
+                                    ctx.seq_ids, ctx.positions, scale, window, sinks, tok0, ntok,
+                                    n_splits=splits, softcap=softcap)
+            return
         ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, v_cache, cache.page_size,
                                 cache.block_tables, ctx.seq_ids, ctx.positions, scale, window, sinks,
                                 tok0, ntok, n_splits=splits, softcap=softcap, value_row=value_row)

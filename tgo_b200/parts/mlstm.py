@@ -26,6 +26,9 @@ from ..kernels import ops
 from ..registry import MIXERS
 from ..weights.binder import WeightSpec
 from .base import LayerCache, Part, StateNeed
+from .retention import step_chunks
+
+USE_CHUNKED = True                   # False: every step through the kernels that walk a request in order
 
 
 class MLSTM(Part):
@@ -75,6 +78,13 @@ class MLSTM(Part):
     def libraries(self, dtype, page_size) -> List[str]:
         return ["sgemm" if dtype == torch.float32 else "gemm_skinny", "layer_ops", "mlstm"]
 
+    def _chunked(self) -> bool:
+        return USE_CHUNKED and ops.mlstm_chunked_supports(self.H, self.dk, self.dv)
+
+    def prepare_capture(self, ctx, cache) -> None:
+        if not ctx.decode_only and self._chunked():
+            step_chunks(ctx, ops.mlstm_chunk_tokens())
+
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         n = sum(extents)
         qk, vw = self.H * self.dk, self.H * self.dv
@@ -92,8 +102,14 @@ class MLSTM(Part):
         q, k, v, gate = z[:, :qk], z[:, qk:2 * qk], z[:, 2 * qk:2 * qk + vw], z[:, 2 * qk + vw:]
         g = ops.linear(x, self.w_gates, out_dtype=torch.float32)       # [T, 2H]: input, forget
         o = torch.empty((x.shape[0], vw), dtype=torch.float32, device=x.device)
-        ops.mlstm(q, k, v, g[:, :H], g[:, H:], self.b_i, self.b_f, self.cap, self.q_scale, o,
-                  ctx.num_seqs, H, dk, dv, ctx.q_start, ctx.state_slots, cache.state)
+        args = (q, k, v, g[:, :H], g[:, H:], self.b_i, self.b_f, self.cap, self.q_scale, o,
+                ctx.num_seqs, H, dk, dv, ctx.q_start, ctx.state_slots, cache.state)
+        if not self._chunked():
+            ops.mlstm(*args)             # a block per (request, head, columns), in order
+        elif ctx.decode_only:
+            ops.mlstm_chunked(*args)     # single tokens: the state streamed through once
+        else:
+            ops.mlstm_chunked(*args, *step_chunks(ctx, ops.mlstm_chunk_tokens()))
         y = torch.empty((x.shape[0], vw), dtype=x.dtype, device=x.device)
         ops.gated_group_norm(o, gate, self.out_gain, y, H, self.eps, "sigmoid", False)
         return ops.linear(y, self.w_o, out_dtype=self.out_dtype)
