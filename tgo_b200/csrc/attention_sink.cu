@@ -36,13 +36,16 @@
 
 // A raw product q . k as the softmax's exponent in base 2: scaled, and with a soft cap c
 // (cap_log2 = c log2 e > 0, scale_over_cap = scale / c) bounded by c tanh(scale (q . k) / c).
-// tanh as 1 - 2 / (1 + e^(2x)) with the hardware's exponential and reciprocal: an absolute error of
-// about 1e-7 (the library's tanhf, many instructions and branches, cost more than the products).
-__device__ __forceinline__ float as_tanh(float x) {
-    return 1.f - __fdividef(2.f, 1.f + exp2f(fminf(x * (2.f * AS_LOG2E), 60.f)));
-}
+// tanh(x) = 1 - 2 / (1 + e^(2x)) with the hardware's exponential and reciprocal, five
+// instructions a score: C tanh(x) = C - 2C / (1 + 2^(2 log2(e) x)); an exponential that
+// overflows gives a reciprocal of 0 and the bound C itself. Absolute error about 1e-7 C (the
+// library's tanhf, many instructions and branches, cost more than the products).
 __device__ __forceinline__ float as_scored(float qk, float scale_log2, float cap_log2, float scale_over_cap) {
-    return cap_log2 > 0.f ? cap_log2 * as_tanh(qk * scale_over_cap) : qk * scale_log2;
+    if (!(cap_log2 > 0.f)) return qk * scale_log2;
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(qk * (scale_over_cap * (2.f * AS_LOG2E))));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+    return fmaf(-2.f * cap_log2, r, cap_log2);
 }
 
 template <int DK, int DV>
@@ -758,6 +761,201 @@ attention_sink_wide_kernel(const bf16* __restrict__ q, long long q_stride, bf16*
     }
 }
 
+// Wide rows, a step of single tokens with at most 16 query heads a kv head: the heads are the
+// rows of one m16 tile that all eight warps hold. Of a 64-key tile warp w makes the scores of keys
+// 8w .. 8w+7 (two accumulators that take the even and the odd 16-channel steps, so that the
+// chain of dependent products is half as long), the warps exchange maxima, sums and P through
+// shared memory, and of O warp w keeps DV / 8 value channels. With n_splits > 1 a CTA's share
+// goes to scratch for the join kernel.
+#define AWD_BN 64
+#define AWD_LDP (AWD_BN + 8)
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AW_WARPS * 32)
+attention_sink_wide_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                                  long long out_stride, const bf16* __restrict__ k_cache, int page_size,
+                                  const int* __restrict__ block_tables, int max_blocks,
+                                  const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
+                                  int Hkv, int dk, int dv, float scale_log2, int window,
+                                  const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
+                                  float* __restrict__ part_ml, float cap_log2, float scale_over_cap) {
+    constexpr int LDK = DK + AS_PAD;
+    constexpr int KS = DK / 16, CHK = DK / 8, WV = DV / AW_WARPS;
+    constexpr int THREADS = AW_WARPS * 32;
+    static_assert(KS % 2 == 0 && WV % 16 == 0, "widths");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [16][LDK]
+    bf16* sk = sq + 16 * LDK;                  // [2][AWD_BN][LDK]
+    bf16* sp = sk + 2 * AWD_BN * LDK;          // [16][AWD_LDP]
+    __shared__ float s_max[AW_WARPS][16], s_sum[AW_WARPS][16];
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = H / Hkv;
+    const int p = positions[tok];
+    if (p < 0) {                               // a request that brings nothing: zeros out
+        if (split == 0)
+            for (int i = tid; i < G * dv; i += THREADS)
+                out[(size_t)tok * out_stride + (size_t)(kvh * G) * dv + i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok] * max_blocks;
+    const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int key_hi = p + 1;
+    int t_lo = key_lo / AWD_BN, t_hi = (key_hi + AWD_BN - 1) / AWD_BN;
+    if (n_splits > 1) {
+        const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
+        t_lo += split * per;
+        if (t_lo + per < t_hi) t_hi = t_lo + per;
+    }
+    const int chk = dk / 8;
+    for (int i = tid; i < 16 * CHK; i += THREADS) {
+        const int r = i / CHK, c = i % CHK;
+        const bool ok = r < G && c < chk;
+        const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * dk + c * 8 : q;
+        cp_async16(sq + r * LDK + c * 8, src, ok);
+    }
+    auto load_k = [&](int t, int buf) {
+        bf16* dks = sk + buf * AWD_BN * LDK;
+        for (int i = tid; i < AWD_BN * CHK; i += THREADS) {
+            const int r = i / CHK, c = i % CHK;
+            const int j = t * AWD_BN + r;
+            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            size_t off = 0;
+            if (ok) {
+                const int pi = j / page_size, po = j - pi * page_size;
+                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk + c * 8;
+            }
+            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+    };
+    if (t_lo < t_hi) load_k(t_lo, 0);
+    cp_async_commit();
+
+    float o[WV / 8][4];
+#pragma unroll
+    for (int i = 0; i < WV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int row_of[2] = {lane >> 2, (lane >> 2) + 8};
+    const bool row_ok[2] = {row_of[0] < G, row_of[1] < G};
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_k(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kt = sk + buf * AWD_BN * LDK;
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+        for (int ks = 0; ks < KS; ks += 2) {
+            uint32_t qa[4], qb[4], kb[4];
+            ldmatrix_x4(qa, sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
+            ldmatrix_x4(qb, sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (ks + 1) * 16 + (lane >> 4) * 8);
+            // four 8 x 8 blocks of this warp's eight keys: channels ks*16 .. ks*16 + 31
+            ldmatrix_x4(kb, kt + (warp * 8 + (lane & 7)) * LDK + ks * 16 + (lane >> 3) * 8);
+            mma_bf16(s0, qa, kb[0], kb[1]);
+            mma_bf16(s1, qb, kb[2], kb[3]);
+        }
+        float s[4], mx[2] = {-INFINITY, -INFINITY};
+        const int kbase = t * AWD_BN + warp * 8 + (lane & 3) * 2;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int j = kbase + e;
+            const bool vis = j >= key_lo && j < key_hi;
+            s[e] = (vis && row_ok[0]) ? as_scored(s0[e] + s1[e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+            s[2 + e] = (vis && row_ok[1]) ? as_scored(s0[2 + e] + s1[2 + e], scale_log2, cap_log2, scale_over_cap)
+                                          : -INFINITY;
+            mx[0] = fmaxf(mx[0], s[e]);
+            mx[1] = fmaxf(mx[1], s[2 + e]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            if ((lane & 3) == 0) s_max[warp][row_of[h]] = mx[h];
+        }
+        __syncthreads();
+        float corr[2], sum[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float mn = m_run[h];
+#pragma unroll
+            for (int w = 0; w < AW_WARPS; ++w) mn = fmaxf(mn, s_max[w][row_of[h]]);
+            const float base = mn == -INFINITY ? 0.f : mn;      // no key seen yet: exp2(-inf - 0) = 0
+            corr[h] = exp2f(m_run[h] - base);
+            m_run[h] = mn;
+            s[2 * h] = exp2f(s[2 * h] - base);
+            s[2 * h + 1] = exp2f(s[2 * h + 1] - base);
+            sum[h] = s[2 * h] + s[2 * h + 1];
+            sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+            sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
+            if ((lane & 3) == 0) s_sum[warp][row_of[h]] = sum[h];
+            *(uint32_t*)(sp + row_of[h] * AWD_LDP + warp * 8 + (lane & 3) * 2) = pack_bf16(s[2 * h], s[2 * h + 1]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < AW_WARPS; ++w) l += s_sum[w][row_of[h]];
+            l_run[h] = l_run[h] * corr[h] + l;
+        }
+#pragma unroll
+        for (int i = 0; i < WV / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < AWD_BN / 16; ++kk) {
+            uint32_t pa[4];
+            ldmatrix_x4(pa, sp + ((lane & 7) + ((lane >> 3) & 1) * 8) * AWD_LDP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int dp = 0; dp < WV / 16; ++dp) {
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + warp * WV +
+                                          dp * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+                mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    const int col = warp * WV + (lane & 3) * 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!row_ok[h]) continue;
+        const int head = kvh * G + row_of[h];
+        float l = l_run[h];
+        if (n_splits > 1) {
+            const size_t at = ((size_t)tok * H + head) * n_splits + split;
+            if ((lane & 3) == 0 && warp == 0) {
+                part_ml[at * 2] = m_run[h];
+                part_ml[at * 2 + 1] = l;
+            }
+            float* po = part_o + at * dv + col;
+#pragma unroll
+            for (int i = 0; i < WV / 8; ++i)
+                if (col + i * 8 < dv) *(float2*)(po + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+            continue;
+        }
+        float c2 = 1.f;
+        if (sinks) {
+            const float sk2 = sinks[head] * AS_LOG2E, m = m_run[h];
+            const float mn = fmaxf(m, sk2);
+            c2 = exp2f(m - mn);
+            l = l * c2 + exp2f(sk2 - mn);
+        }
+        const float inv = l > 0.f ? c2 / l : 0.f;
+        bf16* dst = out + (size_t)tok * out_stride + (size_t)head * dv + col;
+#pragma unroll
+        for (int i = 0; i < WV / 8; ++i)
+            if (col + i * 8 < dv)
+                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    }
+}
+
 // Joins the shares of a token's keys: out = sum_s O_s 2^(m_s - m) / (sum_s l_s 2^(m_s - m) +
 // 2^(sink - m)), m the largest of the maxima and the sink. A block per (token, head).
 __global__ void attention_sink_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -885,9 +1083,23 @@ static int launch_sink_wide(const bf16* q, long long q_stride, bf16* out, long l
     const float scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     const size_t smem = ((size_t)(AW_BM + 2 * AW_BN) * (DK + AS_PAD) + (size_t)AW_BM * AW_LDP) * sizeof(bf16);
     const int G = H / Hkv, GB = G < AW_BM ? G : AW_BM;
+    int rc;
+    if (!tile_tok0 && G <= 16) {               // single tokens, few heads a kv head: all warps on one m16 tile
+        const size_t dsm = ((size_t)(16 + 2 * AWD_BN) * (DK + AS_PAD) + (size_t)16 * AWD_LDP) * sizeof(bf16);
+        auto dec = attention_sink_wide_decode_kernel<DK, DV>;
+        if (dsm > 48 * 1024) cudaFuncSetAttribute(dec, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+        rc = tgo_launch_pdl(dec, dim3(n_tiles, Hkv, n_splits), dim3(AW_WARPS * 32), dsm, stream, q, q_stride, out,
+                            out_stride, k_cache, page_size, block_tables, max_blocks, positions, seq_ids, H, Hkv,
+                            dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o, part_ml, cap_log2,
+                            scale_over_cap);
+        if (rc || n_splits <= 1) return rc;
+        attention_sink_join_kernel<<<dim3(n_tiles, H), 128, 0, stream>>>(part_o, part_ml, positions, sinks, out,
+                                                                        out_stride, H, dv, n_splits);
+        return launch_status();
+    }
     auto kernel = attention_sink_wide_kernel<DK, DV>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    int rc = tgo_launch_pdl(kernel, dim3(n_tiles, Hkv * ((G + GB - 1) / GB), n_splits), dim3(AW_WARPS * 32), smem,
+    rc = tgo_launch_pdl(kernel, dim3(n_tiles, Hkv * ((G + GB - 1) / GB), n_splits), dim3(AW_WARPS * 32), smem,
                             stream, q, q_stride, out, out_stride, k_cache, page_size, block_tables, max_blocks,
                             positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window,
                             sinks, n_splits, part_o, part_ml, cap_log2, scale_over_cap);

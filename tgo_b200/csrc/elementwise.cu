@@ -822,6 +822,97 @@ qk_rownorm_rope_cache_kernel(T* __restrict__ q, long long q_stride, const T* __r
     }
 }
 
+// The same for bfloat16 rows whose widths are multiples of 8 and whose rows start on 16 bytes:
+// 16-byte loads, the row (times its gain) kept in shared memory as float32 between the sum of
+// squares and the rotation, 16-byte stores. row_f: [H dk + Hkv dk] floats of dynamic shared memory.
+__global__ void __launch_bounds__(256)
+qk_rownorm_rope_cache_bf16x8_kernel(bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ k,
+                                    long long k_stride, const bf16* __restrict__ v, long long v_stride, int H,
+                                    int Hkv, int dk, int dv, const float* __restrict__ q_gain,
+                                    const float* __restrict__ k_gain, float eps, const float* __restrict__ rope,
+                                    int rot, int interleaved, const int* __restrict__ slots,
+                                    bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int page_size) {
+    extern __shared__ __align__(16) float row_f[];
+    __shared__ float scratch[33];
+    pdl_wait();
+    const int t = blockIdx.x;
+    bf16* qr = q + (size_t)t * q_stride;
+    const bf16* kr = k ? k + (size_t)t * k_stride : nullptr;
+    const int qw = H * dk, kw = kr ? Hkv * dk : 0;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < (qw + kw) / 8; c += 256) {
+        const bool is_q = c * 8 < qw;
+        const int at = is_q ? c * 8 : c * 8 - qw;
+        const uint4 raw = *(const uint4*)((is_q ? qr : kr) + at);
+        const float* gain = is_q ? q_gain : k_gain;
+        float g[8];
+        if (gain) {
+            *(float4*)g = *(const float4*)(gain + at);
+            *(float4*)(g + 4) = *(const float4*)(gain + at + 4);
+        }
+        const __nv_bfloat162* x2 = (const __nv_bfloat162*)&raw;
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x = __bfloat1622float2(x2[i]);
+            ss += x.x * x.x + x.y * x.y;
+            row_f[c * 8 + 2 * i] = gain ? x.x * g[2 * i] : x.x;
+            row_f[c * 8 + 2 * i + 1] = gain ? x.y * g[2 * i + 1] : x.y;
+        }
+        if (is_q) sq += ss; else sk += ss;
+    }
+    sq = block_sum(sq, scratch);
+    if (kr) sk = block_sum(sk, scratch);
+    const float rq = q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f;
+    const float rk = (k_gain && kr) ? rsqrtf(sk / (float)kw + eps) : 1.f;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    const int half = rot / 2;
+    const float* cs = rope ? rope + (size_t)t * rot : nullptr;
+    const int cpd = dk / 8;                                  // chunks of a head
+    const int nchunks = (qw + (slot >= 0 ? kw : 0)) / 8;
+    for (int c = threadIdx.x; c < nchunks; c += 256) {
+        const bool is_q = c * 8 < qw;
+        const int cc = is_q ? c : c - qw / 8;
+        const int head = cc / cpd, ch0 = (cc % cpd) * 8;
+        const float* src = row_f + (is_q ? 0 : qw) + head * dk;
+        const float r = is_q ? rq : rk;
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int ch = ch0 + i;
+            float x = src[ch] * r;
+            if (cs && ch < rot) {
+                int other, idx;
+                bool first;
+                if (interleaved) { first = !(ch & 1); other = ch ^ 1; idx = ch >> 1; }
+                else { first = ch < half; other = first ? ch + half : ch - half; idx = first ? ch : ch - half; }
+                const float y = src[other] * r;
+                const float cv = cs[idx], sv = cs[half + idx];
+                x = first ? x * cv - y * sv : x * cv + y * sv;
+            }
+            o[i] = x;
+        }
+        uint4 packed;
+        __nv_bfloat162* p2 = (__nv_bfloat162*)&packed;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+        bf16* dst = is_q ? qr + (size_t)head * dk + ch0
+                         : k_cache + (((size_t)page * Hkv + head) * page_size + off) * dk + ch0;
+        *(uint4*)dst = packed;
+    }
+    if (v && slot >= 0) {
+        const bf16* vr = v + (size_t)t * v_stride;
+        const int vpd = dv / 8;
+        for (int c = threadIdx.x; c < Hkv * vpd; c += 256) {
+            const int head = c / vpd, c8 = (c % vpd) * 8;
+            *(uint4*)(v_cache + (((size_t)page * Hkv + head) * page_size + off) * dv + c8) =
+                *(const uint4*)(vr + (size_t)head * dv + c8);
+        }
+    }
+}
+
+
 // q is treated in place; k and v may be null (then only q is); k and v go to the cache only.
 // Gains float32 [H dk] and [Hkv dk], or null for no norm.
 TGO_API int tgo_qk_rownorm_rope_cache(void* q, long long q_stride, const void* k, long long k_stride,
@@ -834,6 +925,19 @@ TGO_API int tgo_qk_rownorm_rope_cache(void* q, long long q_stride, const void* k
     if (dk <= 0 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || H <= 0) return TGO_E_BAD_ARG;
     if ((k || v) && (Hkv <= 0 || page_size <= 0 || !slots || !k_cache)) return TGO_E_BAD_ARG;
     if (v && !v_cache) return TGO_E_BAD_ARG;
+    const size_t row_bytes = ((size_t)H * dk + (k ? (size_t)Hkv * dk : 0)) * sizeof(float);
+    const bool aligned = !(dk % 8) && !(dv % 8) && !(q_stride % 8) && !(k_stride % 8) && !(v_stride % 8) &&
+                         !((uintptr_t)q & 15) && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) &&
+                         !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15) && !((uintptr_t)q_gain & 15) &&
+                         !((uintptr_t)k_gain & 15);
+    if (dtype == TGO_BF16 && aligned && row_bytes <= 96 * 1024) {
+        auto kern = qk_rownorm_rope_cache_bf16x8_kernel;
+        if (row_bytes > 48 * 1024)
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+        return tgo_launch_pdl(kern, dim3(T), dim3(256), row_bytes, stream, (bf16*)q, q_stride, (const bf16*)k,
+                              k_stride, (const bf16*)v, v_stride, H, Hkv, dk, dv, q_gain, k_gain, eps, rope, rot,
+                              interleaved, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+    }
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(qk_rownorm_rope_cache_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)q,
                               q_stride, (const bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dk, dv,

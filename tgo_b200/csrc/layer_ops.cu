@@ -416,6 +416,48 @@ gated_group_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate,
     }
 }
 
+// Groups of up to 512 channels: a warp a (token, group), the group's values in registers between
+// the sum of squares and the scaling, no block-wide sum. Four warps a block.
+#define GGN_PER 16
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_group_norm_warp_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
+                             const float* __restrict__ gain, T* __restrict__ out, int width, int groups,
+                             float eps, int gate_act, int gate_first, long long pairs) {
+    pdl_wait();
+    const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= pairs) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = w / groups;
+    const int g = (int)(w % groups);
+    const int n = width / groups;
+    const float* x = o + (size_t)t * width + (size_t)g * n;
+    const T* gz = gate ? gate + (size_t)t * gate_stride + (size_t)g * n : nullptr;
+    float v[GGN_PER], z[GGN_PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < GGN_PER; ++u) {
+        const int i = lane + 32 * u;
+        v[u] = i < n ? x[i] : 0.f;
+        z[u] = (gz && i < n) ? gate_value(to_f32(gz[i]), gate_act) : 1.f;
+        if (gate_first) v[u] *= z[u];
+        ss += v[u] * v[u];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)n + eps);
+    T* y = out + (size_t)t * width + (size_t)g * n;
+#pragma unroll
+    for (int u = 0; u < GGN_PER; ++u) {
+        const int i = lane + 32 * u;
+        if (i < n) {
+            float a = v[u] * r;
+            if (gain) a *= gain[g * n + i];
+            if (!gate_first) a *= z[u];
+            y[i] = from_f32<T>(a);
+        }
+    }
+}
+
 TGO_API int tgo_gated_group_norm(const float* o, const void* gate, long long gate_stride,
                                  const float* gain, void* out, int dtype, int T, int width,
                                  int groups, float eps, int gate_act, int gate_first,
@@ -424,6 +466,19 @@ TGO_API int tgo_gated_group_norm(const float* o, const void* gate, long long gat
     if (width <= 0 || groups <= 0 || width % groups || groups > 65535 || gate_act < 0 || gate_act > 2)
         return TGO_E_BAD_ARG;
     const int n = width / groups;
+    const long long pairs = (long long)T * groups;
+    if (n <= 32 * GGN_PER && (pairs + 3) / 4 <= 0x7fffffffLL) {
+        const dim3 wgrid((unsigned)((pairs + 3) / 4)), wblock(128);
+        if (dtype == TGO_BF16)
+            return tgo_launch_pdl(gated_group_norm_warp_kernel<bf16>, wgrid, wblock, 0, stream, o,
+                                  (const bf16*)gate, gate_stride, gain, (bf16*)out, width, groups, eps, gate_act,
+                                  gate_first, pairs);
+        if (dtype == TGO_F32)
+            return tgo_launch_pdl(gated_group_norm_warp_kernel<float>, wgrid, wblock, 0, stream, o,
+                                  (const float*)gate, gate_stride, gain, (float*)out, width, groups, eps,
+                                  gate_act, gate_first, pairs);
+        return TGO_E_BAD_ARG;
+    }
     const int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
     const dim3 grid(T, groups), block(threads);
     if (dtype == TGO_BF16)

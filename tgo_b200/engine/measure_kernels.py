@@ -428,11 +428,16 @@ def measure_derosun_kernels(width: int, heads: int, kv_heads: int, key_dim: int,
                 like_ms = _timed(lambda: ops.attention_flash(q, o, H, G, dk, kc, vc, page, table, ctx.positions,
                                                              ctx.seq_ids, None, None, scale, 0,
                                                              n_splits=n_splits), flush)
+        ms0 = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, 0, None), flush)
         if extent > 1:
             row(f"attention with capped scores, {what}", ms, like, like_ms, "tensor",
                 2.0 * H * (dk + dv) * (prompt * (prompt + 1) / 2))
+            row(f"the same kernel without the cap, {what}", ms0, None, 0.0, "tensor",
+                2.0 * H * (dk + dv) * (prompt * (prompt + 1) / 2))
         else:
             row(f"attention with capped scores, {what}", ms, like, like_ms, "hbm",
+                2.0 * n_req * context * G * (dk + dv))
+            row(f"the same kernel without the cap, {what}", ms0, None, 0.0, "hbm",
                 2.0 * n_req * context * G * (dk + dv))
     # ---- projection rows: norm over the whole row, banded rotation, cache write
     T = prompt
