@@ -599,18 +599,31 @@ attention_sink_wide_kernel(const bf16* __restrict__ q, long long q_stride, bf16*
         const bf16* src = ok ? q + (size_t)(tok0 + r / GB) * q_stride + (size_t)(kvh * G + h0 + r % GB) * dk + c * 8 : q;
         cp_async16(sq + r * LDK + c * 8, src, ok);
     }
+    // a warp a row, the row's place in the cache worked out once for its chunks; the rows'
+    // block-table reads go out together, ahead of the copies
     auto load_k = [&](int t, int buf) {
         bf16* dks = sk + buf * AW_BN * LDK;
-        for (int i = tid; i < AW_BN * CHK; i += THREADS) {
-            const int r = i / CHK, c = i % CHK;
-            const int j = t * AW_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chk;
-            size_t off = 0;
-            if (ok) {
+        constexpr int RPW = AW_BN / AW_WARPS;
+        size_t base[RPW];
+        bool in[RPW];
+#pragma unroll
+        for (int x = 0; x < RPW; ++x) {
+            const int j = t * AW_BN + warp + x * AW_WARPS;
+            in[x] = j >= key_lo && j < key_hi;
+            base[x] = 0;
+            if (in[x]) {
                 const int pi = j / page_size, po = j - pi * page_size;
-                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk + c * 8;
+                base[x] = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk;
             }
-            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+#pragma unroll
+        for (int x = 0; x < RPW; ++x) {
+            const int r = warp + x * AW_WARPS;
+#pragma unroll
+            for (int c = lane; c < CHK; c += 32) {
+                const bool ok = in[x] && c < chk;
+                cp_async16(dks + r * LDK + c * 8, k_cache + (ok ? base[x] + c * 8 : 0), ok);
+            }
         }
     };
     if (t_lo < t_hi) load_k(t_lo, 0);
@@ -763,8 +776,8 @@ attention_sink_wide_kernel(const bf16* __restrict__ q, long long q_stride, bf16*
 
 // Wide rows, a step of single tokens with at most 16 query heads a kv head: the heads are the
 // rows of one m16 tile that all eight warps hold. Of a 64-key tile warp w makes the scores of keys
-// 8w .. 8w+7 (two accumulators that take the even and the odd 16-channel steps, so that the
-// chain of dependent products is half as long), the warps exchange maxima, sums and P through
+// 8w .. 8w+7 (four accumulators that take every fourth 16-channel step, so that the chain of
+// dependent products is a quarter as long), the warps exchange maxima, sums and P through
 // shared memory, and of O warp w keeps DV / 8 value channels. With n_splits > 1 a CTA's share
 // goes to scratch for the join kernel.
 #define AWD_BN 64
@@ -782,7 +795,7 @@ attention_sink_wide_decode_kernel(const bf16* __restrict__ q, long long q_stride
     constexpr int LDK = DK + AS_PAD;
     constexpr int KS = DK / 16, CHK = DK / 8, WV = DV / AW_WARPS;
     constexpr int THREADS = AW_WARPS * 32;
-    static_assert(KS % 2 == 0 && WV % 16 == 0, "widths");
+    static_assert(KS % 4 == 0 && WV % 16 == 0, "widths");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sq = (bf16*)smem_raw;                // [16][LDK]
     bf16* sk = sq + 16 * LDK;                  // [2][AWD_BN][LDK]
@@ -815,18 +828,31 @@ attention_sink_wide_decode_kernel(const bf16* __restrict__ q, long long q_stride
         const bf16* src = ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * dk + c * 8 : q;
         cp_async16(sq + r * LDK + c * 8, src, ok);
     }
+    // a warp a row, the row's place in the cache worked out once for its chunks; the rows'
+    // block-table reads go out together, ahead of the copies
     auto load_k = [&](int t, int buf) {
         bf16* dks = sk + buf * AWD_BN * LDK;
-        for (int i = tid; i < AWD_BN * CHK; i += THREADS) {
-            const int r = i / CHK, c = i % CHK;
-            const int j = t * AWD_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chk;
-            size_t off = 0;
-            if (ok) {
+        constexpr int RPW = AWD_BN / AW_WARPS;
+        size_t base[RPW];
+        bool in[RPW];
+#pragma unroll
+        for (int x = 0; x < RPW; ++x) {
+            const int j = t * AWD_BN + warp + x * AW_WARPS;
+            in[x] = j >= key_lo && j < key_hi;
+            base[x] = 0;
+            if (in[x]) {
                 const int pi = j / page_size, po = j - pi * page_size;
-                off = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk + c * 8;
+                base[x] = (((size_t)bt[pi] * Hkv + kvh) * page_size + po) * dk;
             }
-            cp_async16(dks + r * LDK + c * 8, k_cache + off, ok);
+        }
+#pragma unroll
+        for (int x = 0; x < RPW; ++x) {
+            const int r = warp + x * AW_WARPS;
+#pragma unroll
+            for (int c = lane; c < CHK; c += 32) {
+                const bool ok = in[x] && c < chk;
+                cp_async16(dks + r * LDK + c * 8, k_cache + (ok ? base[x] + c * 8 : 0), ok);
+            }
         }
     };
     if (t_lo < t_hi) load_k(t_lo, 0);
@@ -847,16 +873,24 @@ attention_sink_wide_decode_kernel(const bf16* __restrict__ q, long long q_stride
         __syncthreads();
         const bf16* kt = sk + buf * AWD_BN * LDK;
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-        for (int ks = 0; ks < KS; ks += 2) {
-            uint32_t qa[4], qb[4], kb[4];
-            ldmatrix_x4(qa, sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
-            ldmatrix_x4(qb, sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (ks + 1) * 16 + (lane >> 4) * 8);
-            // four 8 x 8 blocks of this warp's eight keys: channels ks*16 .. ks*16 + 31
-            ldmatrix_x4(kb, kt + (warp * 8 + (lane & 7)) * LDK + ks * 16 + (lane >> 3) * 8);
-            mma_bf16(s0, qa, kb[0], kb[1]);
-            mma_bf16(s1, qb, kb[2], kb[3]);
+        float s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16* qrow = sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8;
+        const bf16* krow = kt + (warp * 8 + (lane & 7)) * LDK + (lane >> 3) * 8;
+#pragma unroll 3
+        for (int ks = 0; ks < KS; ks += 4) {
+            uint32_t qa[4][4], kb[2][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) ldmatrix_x4(qa[u], qrow + (ks + u) * 16);
+            // four 8 x 8 blocks of this warp's eight keys a load: 32 channels
+            ldmatrix_x4(kb[0], krow + ks * 16);
+            ldmatrix_x4(kb[1], krow + (ks + 2) * 16);
+            mma_bf16(s0, qa[0], kb[0][0], kb[0][1]);
+            mma_bf16(s1, qa[1], kb[0][2], kb[0][3]);
+            mma_bf16(s2, qa[2], kb[1][0], kb[1][1]);
+            mma_bf16(s3, qa[3], kb[1][2], kb[1][3]);
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s0[e] += s2[e]; s1[e] += s3[e]; }
         float s[4], mx[2] = {-INFINITY, -INFINITY};
         const int kbase = t * AWD_BN + warp * 8 + (lane & 3) * 2;
 #pragma unroll

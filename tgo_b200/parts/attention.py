@@ -76,29 +76,32 @@ def step_tiles_and_singles(ctx, tokens_per_tile: int):
     return got
 
 
-def splits_for(pairs: int, reach: int, window: int, num_sms: int, ctas_per_sm: int = 3) -> int:
+def splits_for(pairs: int, reach: int, window: int, num_sms: int, ctas_per_sm: int = 3,
+               start: float = 5.0, join: float = 10.0) -> int:
     """How many CTAs share one (request, kv head) pair's keys in a decode step: the count
     that is cheapest by a small model fitted on B200 (8 kv heads, contexts of 1024 and 4096,
     batches 8 to 128): the CTAs run in rounds of as many as the GPU holds, a CTA costs 1 unit
     per 64-key tile and 5 to start, joining the splits costs 10 once. So a few requests are
     cut until they fill the GPU once (batch 8: 7 ways), 32 or 64 requests of 1024 keys are
     not cut (the start is paid once), and 64 requests of 4096 keys are cut in 3 or 4, because
-    the second, nearly empty round of whole requests would cost a whole request's time."""
+    the second, nearly empty round of whole requests would cost a whole request's time.
+    `ctas_per_sm`, `start` and `join` (in tiles) describe the kernel: the defaults are the
+    plain decode kernel's; a kernel with heavier tiles has a cheaper start and join."""
     tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
     pairs = max(1, pairs)
     wave = num_sms * ctas_per_sm
     best, best_cost = 1, None
     for s in range(1, max(1, min(tiles // 2, 64)) + 1):
         rounds = -(-pairs * s // wave)
-        cost = rounds * (tiles / s * 1.0 + 5.0) + (10.0 if s > 1 else 0.0)
+        cost = rounds * (tiles / s * 1.0 + start) + (join if s > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
 
 
-def decode_splits(ctx, num_kv_heads: int, window: int, device) -> int:
+def decode_splits(ctx, num_kv_heads: int, window: int, device, **kernel) -> int:
     reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
-    return splits_for(ctx.num_seqs * num_kv_heads, reach, window, ops.num_sms(device))
+    return splits_for(ctx.num_seqs * num_kv_heads, reach, window, ops.num_sms(device), **kernel)
 
 
 def tc_kernel_takes(q_dtype, head_dim: int, group: int, page_size: int) -> bool:

@@ -179,12 +179,16 @@ def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, sof
     form, tokens = tile_form(H, Hkv, dk, dv, value_row, q.dtype)
     if form is not None and ops.attention_sink_takes(q, out):
         tok0, ntok = (None, None) if ctx.decode_only else step_tiles(ctx, tokens)
-        splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
         if form == "wide":
+            # one block a multiprocessor, tiles of rows several times as wide: by the sweep over
+            # shares at batches 8 and 64, a start costs about one tile and the join two
+            splits = decode_splits(ctx, Hkv, window, q.device, ctas_per_sm=1, start=1.0, join=2.0) \
+                if ctx.decode_only else 1
             ops.attention_sink_wide(q, out, H, Hkv, dk, dv, cache.k, cache.page_size, cache.block_tables,
                                     ctx.seq_ids, ctx.positions, scale, window, sinks, tok0, ntok,
                                     n_splits=splits, softcap=softcap)
             return
+        splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
         ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, v_cache, cache.page_size,
                                 cache.block_tables, ctx.seq_ids, ctx.positions, scale, window, sinks,
                                 tok0, ntok, n_splits=splits, softcap=softcap, value_row=value_row)
