@@ -126,7 +126,7 @@ def _paged(rows, page_size, table, pages_total, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,a,b,rot,ps", [(4, 2, 12, 20, 8, 8), (1, 1, 24, 24, 24, 16), (6, 3, 10, 6, 6, 4),
-                                            (8, 1, 64, 64, 16, 16), (5, 5, 8, 8, 0, 4)])
+                                            (8, 2, 64, 48, 32, 16), (5, 5, 8, 8, 0, 4)])
 def test_rows_normed_whole_rotated_in_bands_and_stored(H, G, a, b, rot, ps, dtype):
     """q and k normed over ALL their heads at once (a norm per head gives other numbers), the
     first `rot` channels of every head turned in half-split pairs with banded frequencies, k
@@ -196,7 +196,7 @@ def _run_attention(fn, q, k, v, H, b, ps, dtype, positions, one_plane=False):
     return out
 
 
-CAP_SIZES = [(4, 2, 12, 20, 8), (8, 1, 64, 64, 16), (3, 3, 16, 8, 4), (6, 2, 88, 72, 16), (1, 1, 24, 24, 16)]
+CAP_SIZES = [(4, 2, 12, 20, 8), (8, 2, 64, 48, 16), (3, 3, 16, 8, 4), (6, 2, 88, 72, 16), (1, 1, 24, 24, 16)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -225,7 +225,7 @@ def test_capped_scores_generic(H, G, a, b, ps, dtype):
     assert np.abs(plain.capped_softmax_attention(q2, k2, v2, 0.3, 2.5)[299] - capped).max() > 0.02
 
 
-TILE_CAP_SIZES = [(4, 2, 16, 24, 8), (8, 1, 64, 64, 16), (6, 2, 88, 72, 16), (2, 2, 128, 128, 16),
+TILE_CAP_SIZES = [(4, 2, 16, 24, 8), (12, 1, 64, 48, 16), (6, 2, 88, 72, 16), (2, 2, 128, 128, 16),
                   (40, 1, 8, 16, 16), (5, 5, 40, 40, 8)]
 
 
@@ -367,7 +367,7 @@ def test_latent_rows_normed_rotated_and_stored(rank, width, rot, ps, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T", [1, 9, 70])
-@pytest.mark.parametrize("H,K,N", [(3, 12, 20), (5, 7, 11), (8, 32, 64), (1, 16, 40)])
+@pytest.mark.parametrize("H,K,N", [(3, 12, 20), (5, 7, 11), (8, 24, 72), (1, 16, 40)])
 def test_a_product_per_head_and_the_rotated_slice(H, K, N, T, dtype):
     """y_h = W_h x_h into rows wider than the result (the rest is another kernel's), and a slice
     of every head copied and turned beside it: together the query as the latent cache sees it."""
@@ -390,7 +390,7 @@ def test_a_product_per_head_and_the_rotated_slice(H, K, N, T, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("form", ["in order", "by chunks"])
-@pytest.mark.parametrize("H,dk,dv", [(3, 8, 12), (1, 24, 24), (2, 5, 7), (2, 32, 64), (4, 16, 40), (2, 128, 72)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 8, 12), (1, 24, 24), (2, 5, 7), (2, 32, 48), (4, 16, 40), (2, 128, 72)])
 def test_matrix_memory_over_portions_and_slots(H, dk, dv, form, dtype):
     """Three requests of unequal length in one call, then each continued in portions that end
     before, on and after the kernels' chunks of tokens, in state slots given out of order, by
