@@ -266,7 +266,8 @@ def test_capped_scores_on_the_tensor_cores(H, G, a, b, ps):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,rank,width,ps,tile", [(3, 20, 8, 8, False), (20, 48, 16, 16, True),
                                                   (4, 32, 32, 16, True), (5, 11, 6, 4, False),
-                                                  (1, 40, 2, 16, False), (16, 96, 32, 16, True)])
+                                                  (1, 40, 2, 16, False), (16, 96, 32, 16, True),
+                                                  (2, 700, 20, 16, False)])
 def test_attention_whose_values_are_the_head_of_its_key_rows(H, rank, width, ps, tile, dtype):
     """One cache plane, rows rank + width wide: the key is the whole row, the value its first
     `rank` channels. A far loud row must be found; the channels after `rank` must not leak."""

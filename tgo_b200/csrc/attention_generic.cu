@@ -1,4 +1,5 @@
-// Paged causal attention, one warp per (token, head), any head size up to 256 and any
+// Paged causal attention, one warp per (token, head), any head size up to 256 (rows whose
+// values lie inside the keys: up to 1152) and any
 // storage type. It is the float32 path's attention and the fallback of the bfloat16
 // path for head sizes that the tensor-core kernels do not take.
 //
@@ -18,6 +19,7 @@
 
 #define AG_MAX_DH 256            // rows up to this wide take the instance with 8 sums a lane
 #define AG_MAX_WIDE 640          // wider ones, up to this, the instance with 20
+#define AG_MAX_WIDEST 1152       // and up to this (a latent of 1024 with its rotated part), 36
 #define AG_WARPS 4
 
 template <typename T, int NACC>
@@ -103,10 +105,10 @@ TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
                                   const float* sinks, float softcap, int v_row, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (v_row <= 0) v_row = dv;
-    if (dh <= 0 || dh > AG_MAX_WIDE || dv <= 0 || dv > AG_MAX_WIDE || H <= 0 || Hkv <= 0 || H % Hkv ||
+    if (dh <= 0 || dh > AG_MAX_WIDEST || dv <= 0 || dv > AG_MAX_WIDEST || H <= 0 || Hkv <= 0 || H % Hkv ||
         page_size <= 0 || max_blocks <= 0 || window < 0 || v_row < dv || !(softcap >= 0.f))
         return TGO_E_BAD_ARG;
-    const bool wide = dv > AG_MAX_DH;
+    const bool wide = dv > AG_MAX_DH, widest = dv > AG_MAX_WIDE;
     const dim3 grid(T, (H + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * dh * sizeof(float);
 #define AG_GO(TT, NACC)                                                                            \
@@ -115,9 +117,9 @@ TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
         (const TT*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale, window,   \
         sinks, softcap, v_row)
     if (dtype == TGO_BF16) {
-        if (wide) AG_GO(bf16, AG_MAX_WIDE / 32); else AG_GO(bf16, AG_MAX_DH / 32);
+        if (widest) AG_GO(bf16, AG_MAX_WIDEST / 32); else if (wide) AG_GO(bf16, AG_MAX_WIDE / 32); else AG_GO(bf16, AG_MAX_DH / 32);
     } else if (dtype == TGO_F32) {
-        if (wide) AG_GO(float, AG_MAX_WIDE / 32); else AG_GO(float, AG_MAX_DH / 32);
+        if (widest) AG_GO(float, AG_MAX_WIDEST / 32); else if (wide) AG_GO(float, AG_MAX_WIDE / 32); else AG_GO(float, AG_MAX_DH / 32);
     } else
         return TGO_E_BAD_ARG;
 #undef AG_GO

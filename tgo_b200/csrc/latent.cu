@@ -171,11 +171,58 @@ head_linear_kernel(const T* __restrict__ x, long long x_stride, int x_head, cons
     }
 }
 
+// Up to 16 rows (a step of a few single tokens; with more, walking the rows costs more than the
+// tiles below) and K up to 512: a warp an output of one head. A lane holds
+// the weights k = lane, lane + 32, ... of its output in registers and walks the tokens, four at
+// a time; the lanes' partial sums are joined by shuffles in a fixed order, so an output's bits
+// depend on nothing but its own row. The weights are read once, 64 bytes a warp and load.
+#define HLF_PER 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_linear_few_kernel(const T* __restrict__ x, long long x_stride, int x_head, const T* __restrict__ w,
+                       T* __restrict__ y, long long y_stride, int y_head, int Tn, int N, int K) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), h = blockIdx.y;
+    if (n >= N) return;
+    const T* wr = w + ((size_t)h * N + n) * K;
+    float wv[HLF_PER];
+#pragma unroll
+    for (int i = 0; i < HLF_PER; ++i) wv[i] = lane + 32 * i < K ? to_f32(wr[lane + 32 * i]) : 0.f;
+    for (int t0 = 0; t0 < Tn; t0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (t0 + u < Tn) {
+                const T* xr = x + (size_t)(t0 + u) * x_stride + (size_t)h * x_head;
+#pragma unroll
+                for (int i = 0; i < HLF_PER; ++i)
+                    if (lane + 32 * i < K) acc[u] += wv[i] * to_f32(xr[lane + 32 * i]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float a = warp_sum(acc[u]);
+            if (lane == 0 && t0 + u < Tn) y[(size_t)(t0 + u) * y_stride + (size_t)h * y_head + n] = from_f32<T>(a);
+        }
+    }
+}
+
 TGO_API int tgo_head_linear(const void* x, long long x_stride, int x_head, const void* w, void* y,
                             long long y_stride, int y_head, int dtype, int T, int H, int N, int K,
                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || N <= 0 || K <= 0 || H > 65535) return TGO_E_BAD_ARG;
+    if (T <= 16 && K <= 32 * HLF_PER && (N + 7) / 8 <= 0x7fffffff) {
+        const dim3 fgrid((N + 7) / 8, H), fblock(256);
+        if (dtype == TGO_BF16)
+            return tgo_launch_pdl(head_linear_few_kernel<bf16>, fgrid, fblock, 0, stream, (const bf16*)x, x_stride,
+                                  x_head, (const bf16*)w, (bf16*)y, y_stride, y_head, T, N, K);
+        if (dtype == TGO_F32)
+            return tgo_launch_pdl(head_linear_few_kernel<float>, fgrid, fblock, 0, stream, (const float*)x,
+                                  x_stride, x_head, (const float*)w, (float*)y, y_stride, y_head, T, N, K);
+        return TGO_E_BAD_ARG;
+    }
     const long long blocks64 = (long long)((T + HL_TOK - 1) / HL_TOK) * H * ((N + 63) / 64);
     const int hn = blocks64 < 600 ? 16 : 64;
     const dim3 grid((T + HL_TOK - 1) / HL_TOK, H, (N + hn - 1) / hn), block(256);

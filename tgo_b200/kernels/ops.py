@@ -704,8 +704,10 @@ HEAD_LINEAR_LIBRARY_ROWS = 65     # bfloat16 steps of this many rows or more: th
 def head_linear(x: torch.Tensor, x_head: int, w: torch.Tensor, y: torch.Tensor, y_head: int) -> None:
     """A product per head: y[t, h * y_head + n] = sum_k x[t, h * x_head + k] w[h, n, k], with
     w [H, N, K]; x and y 2-D views with unit column stride. float32, and bfloat16 with few
-    rows: this package's kernel (k summed in order); bfloat16 with many rows: the library's
-    batched product, where the dense products of as many rows take the library too."""
+    rows: this package's kernels (up to 16 rows and K up to 512: a warp an output, the lanes'
+    partial sums joined in a fixed order; else tiles, k summed in order); bfloat16 with many
+    rows: the library's batched product, where the dense products of as many rows take the
+    library too."""
     _need_cuda(x, w, y)
     T = x.shape[0]
     H, N, K = w.shape
