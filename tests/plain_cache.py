@@ -139,8 +139,10 @@ class CacheManager:
         table = req.tables[g]
         if self.groups[g].kind == "full":        # no holes: only the tail can be missing
             return list(range(len(table), last))
-        first = self.groups[g].first_live_position(req.length) // self.page_size
-        return [i for i in range(first, last) if i >= len(table) or table[i] == NULL_PAGE]
+        kept = min(self.pages_for(getattr(self.groups[g], "keep_first", 0)), last)
+        first = max(self.groups[g].first_live_position(req.length) // self.page_size, kept)
+        return [i for i in list(range(kept)) + list(range(first, last))
+                if i >= len(table) or table[i] == NULL_PAGE]
 
     def can_hold(self, n_tokens: int, step_tokens: int = 1) -> bool:
         """Could a request of this many tokens ever fit, with the pools empty, when it is run
@@ -150,7 +152,8 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             need = self.pages_for(n_tokens)
             if grp.kind == "window":
-                need = min(need, self.pages_for(grp.window - 1 + max(1, step_tokens)) + 1)
+                need = min(need, self.pages_for(grp.window - 1 + max(1, step_tokens)) + 1 +
+                           self.pages_for(getattr(grp, "keep_first", 0)))
             if need > self.pools[g].num_pages:
                 return False
         return True
@@ -217,7 +220,7 @@ class CacheManager:
             dead = grp.first_live_position(new_length) // self.page_size
             table = req.tables[g]
             gone = []
-            for i in range(min(dead, len(table))):
+            for i in range(self.pages_for(getattr(grp, "keep_first", 0)), min(dead, len(table))):
                 if table[i] != NULL_PAGE:
                     gone.append(table[i])
                     table[i] = NULL_PAGE

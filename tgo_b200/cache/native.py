@@ -123,6 +123,11 @@ class NativeCacheManager:
             _ptr(_ints(pages_per_group)), c_int(num_slots)))
         if not self._h:
             raise ValueError("cache: the native books refused these sizes")
+        for g, grp in enumerate(groups):
+            if getattr(grp, "keep_first", 0):
+                if self._lib.tgo_cache_set_keep_first(self._h, c_int(g), c_int(grp.keep_first)):
+                    raise ValueError("cache: the native books refused the kept first tokens of "
+                                     f"group {g}")
         self.pools = [_PoolView(self, g) for g in range(len(groups))]
         self.slots = _SlotsView(self, num_slots)
         self.requests: Dict[object, NativeRequest] = {}

@@ -33,14 +33,18 @@ class GroupLayout:
     size])."""
 
     def __init__(self, kind: str, window: Optional[int], planes: int, row_shape: Tuple[int, ...],
-                 calls: List[int], plane_shapes: Optional[Tuple[Tuple[int, ...], ...]] = None):
+                 calls: List[int], plane_shapes: Optional[Tuple[Tuple[int, ...], ...]] = None,
+                 keep_first: int = 0):
         if kind not in ("full", "window"):
             raise ValueError(f"cache: unknown group kind {kind!r}")
         if kind == "window" and (window is None or window <= 0):
             raise ValueError("cache: a window group needs a positive window")
         if planes <= 0 or not row_shape or any(int(n) <= 0 for n in row_shape):
             raise ValueError(f"cache: a group of {planes} planes with rows of {row_shape}")
+        if keep_first < 0 or (keep_first and kind != "window"):
+            raise ValueError("cache: kept first tokens belong to a window group")
         self.kind, self.window = kind, window
+        self.keep_first = int(keep_first)      # a window group: first tokens whose pages stay
         self.planes, self.row_shape = int(planes), tuple(int(n) for n in row_shape)
         self.calls = list(calls)
         # planes whose rows differ (keys wider than values): one row shape per plane
@@ -53,7 +57,8 @@ class GroupLayout:
                 self.plane_shapes = shapes
 
     def key(self):
-        return (self.kind, self.window, self.planes, self.row_shape, self.plane_shapes)
+        return (self.kind, self.window, self.planes, self.row_shape, self.plane_shapes,
+                self.keep_first)
 
     @property
     def uniform(self) -> bool:

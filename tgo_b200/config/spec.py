@@ -109,6 +109,20 @@ class MixerSpec:
     rope_dim: int = 0
     # gated recurrences: the bound c of a gate's pre-activation, c tanh(x / c)
     gate_cap: float = 0.0
+    # attention kinds with a window: the first `keep_first` tokens of a request stay visible to
+    # every later query, at their true positions
+    keep_first: int = 0
+    # attention kinds: every q and k head divided by its root mean square AFTER the rotation,
+    # no gain (eps is norm_eps); and, with conv_taps > 0, q, k and v each through a causal
+    # convolution of that many taps over time, straight after their projections
+    qk_unit_norm: bool = False
+    # attention kinds: (coef, every): the query at position p is multiplied by
+    # 1 + coef * ln(floor((p + 1) / every) + 1); None: no such factor
+    query_temperature: Optional[tuple] = None
+    # attention kinds: a learned bias by distance, a table [rows, heads] (role distance_bias)
+    # whose row for distance n is n below rows/2 and then grows by logarithmic steps up to
+    # this distance, beyond which the last row stands; None: no bias
+    distance_bias_max: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -127,6 +141,14 @@ class FeedForwardSpec:
     router_bias: bool = False
     shared: Optional["FeedForwardSpec"] = None
     bias: bool = False                   # dense kinds: every projection carries a bias
+    # routed kinds: experts without a gate matrix (down act(up x)) when False
+    gated: bool = True
+    # routed kinds: "chosen": softmax over the chosen logits; "all": softmax over every logit,
+    # the chosen scores divided by their sum
+    router_scores: str = "chosen"
+    router_correction: bool = False      # a per-expert term added to the scores for the choice only
+    identity_experts: int = 0            # router outputs past `experts` whose expert is the input itself
+    shared_gate: bool = False            # the shared feed-forward times a logistic gate per token
 
 
 @dataclass(frozen=True)
@@ -144,6 +166,9 @@ class LayerSpec:
     # blocks that norm the sum: the factor on the stream in stream <- norm(factor * stream +
     # sublayer(stream))
     residual_scale: float = 1.0
+    # blocks that keep several copies of the residual stream and learn how the sublayers read
+    # and write them: how many
+    streams: int = 1
 
 
 @dataclass(frozen=True)

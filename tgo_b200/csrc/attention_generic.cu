@@ -15,6 +15,12 @@
 // A value row starts `v_row` elements after the one before it: dv for a plane of values; the
 // key rows' width when a value is the first dv channels of its key row (one cache plane that
 // serves as both, v_cache = k_cache).
+// `keep_first` > 0 (with a window): the first keep_first keys of the request stay visible to
+// every later query, at their true positions, beside the window. The keys are then walked as
+// one list (the kept ones that lie before the window, then the window), 32 at a time, so the
+// order of the sums still depends on (p, window, keep_first) alone.
+// `dist_bias` (float32 [n_dist][H]): dist_bias[min(p - j, n_dist - 1)][h] is added to the
+// scaled score of key j, unscaled (a learned bias by distance).
 #include "common.cuh"
 
 #define AG_MAX_DH 256            // rows up to this wide take the instance with 8 sums a lane
@@ -28,7 +34,8 @@ __global__ void attention_generic_kernel(
     int H, int Hkv, int dh, int dv, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     int page_size, const int* __restrict__ block_tables, int max_blocks,
     const int* __restrict__ seq_ids, const int* __restrict__ positions, float scale, int window,
-    const float* __restrict__ sinks, float softcap, int v_row) {
+    const float* __restrict__ sinks, float softcap, int v_row, int keep_first,
+    const float* __restrict__ dist_bias, int n_dist) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -49,27 +56,31 @@ __global__ void attention_generic_kernel(
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
-    for (int base = lo; base <= p; base += 32) {
-        const int j = base + lane;
-        const int nvalid = (p - base + 1) < 32 ? (p - base + 1) : 32;
+    const int nkept = keep_first < lo ? keep_first : lo;       // kept keys that lie before the window
+    const int nkeys = p >= 0 ? nkept + (p - lo + 1) : 0;
+    for (int vbase = 0; vbase < nkeys; vbase += 32) {
+        const int vj = vbase + lane;
+        const int j = vj < nkept ? vj : lo + (vj - nkept);
+        const int nvalid = (nkeys - vbase) < 32 ? (nkeys - vbase) : 32;
         float s = -INFINITY;
-        if (j <= p) {
+        if (vj < nkeys) {
             const int page = bt[j / page_size];
             const T* kr = k_cache + (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * dh;
             float a = 0.f;
             for (int d = 0; d < dh; ++d) a += qs[d] * to_f32(kr[d]);
             s = a * scale;
             if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            if (dist_bias) s += dist_bias[(size_t)((p - j) < n_dist ? (p - j) : n_dist - 1) * H + h];
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);          // m = -inf the first time: corr = 0
-        const float w = j <= p ? expf(s - m_new) : 0.f;
+        const float w = vj < nkeys ? expf(s - m_new) : 0.f;
         l = l * corr + warp_sum(w);
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[i] *= corr;
         for (int jj = 0; jj < nvalid; ++jj) {
             const float wj = __shfl_sync(0xffffffffu, w, jj);
-            const int kj = base + jj;
+            const int kj = (vbase + jj) < nkept ? vbase + jj : lo + (vbase + jj - nkept);
             const int page = bt[kj / page_size];
             const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + (kj % page_size)) * v_row;
 #pragma unroll
@@ -102,11 +113,13 @@ TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
                                   const void* k_cache, const void* v_cache, int page_size,
                                   const int* block_tables, int max_blocks, const int* seq_ids,
                                   const int* positions, float scale, int window,
-                                  const float* sinks, float softcap, int v_row, cudaStream_t stream) {
+                                  const float* sinks, float softcap, int v_row, int keep_first,
+                                  const float* dist_bias, int n_dist, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (v_row <= 0) v_row = dv;
     if (dh <= 0 || dh > AG_MAX_WIDEST || dv <= 0 || dv > AG_MAX_WIDEST || H <= 0 || Hkv <= 0 || H % Hkv ||
-        page_size <= 0 || max_blocks <= 0 || window < 0 || v_row < dv || !(softcap >= 0.f))
+        page_size <= 0 || max_blocks <= 0 || window < 0 || v_row < dv || !(softcap >= 0.f) || keep_first < 0 ||
+        (dist_bias && n_dist <= 0))
         return TGO_E_BAD_ARG;
     const bool wide = dv > AG_MAX_DH, widest = dv > AG_MAX_WIDE;
     const dim3 grid(T, (H + AG_WARPS - 1) / AG_WARPS);
@@ -115,7 +128,7 @@ TGO_API int tgo_attention_generic(const void* q, long long q_stride, void* out,
     attention_generic_kernel<TT, NACC><<<grid, AG_WARPS * 32, smem, stream>>>(                         \
         (const TT*)q, q_stride, (TT*)out, out_stride, H, Hkv, dh, dv, (const TT*)k_cache,              \
         (const TT*)v_cache, page_size, block_tables, max_blocks, seq_ids, positions, scale, window,   \
-        sinks, softcap, v_row)
+        sinks, softcap, v_row, keep_first, dist_bias, n_dist)
     if (dtype == TGO_BF16) {
         if (widest) AG_GO(bf16, AG_MAX_WIDEST / 32); else if (wide) AG_GO(bf16, AG_MAX_WIDE / 32); else AG_GO(bf16, AG_MAX_DH / 32);
     } else if (dtype == TGO_F32) {

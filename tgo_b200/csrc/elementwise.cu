@@ -744,6 +744,15 @@ TGO_API int tgo_qkv_bias_rope_cache(void* q, long long q_stride, void* k, long l
 // `rot` singly, so q can be written back in place; k goes to its cache plane
 // [page][kv head][offset][dk], v (untouched) to [page][kv head][offset][dv]. Sums, gains and
 // the rotation are float32.
+// A query temperature that grows with the position p: q is multiplied by
+// 1 + coef * ln(floor((p + 1) / every) + 1). Without positions: 1.
+__device__ __forceinline__ float query_temperature(const int* positions, int t, float coef, int every) {
+    if (!positions || every <= 0) return 1.f;
+    const int p = positions[t];
+    if (p < 0) return 1.f;
+    return 1.f + coef * logf((float)((p + 1) / every + 1));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_rownorm_rope_cache_kernel(T* __restrict__ q, long long q_stride, const T* __restrict__ k,
@@ -752,7 +761,8 @@ qk_rownorm_rope_cache_kernel(T* __restrict__ q, long long q_stride, const T* __r
                              const float* __restrict__ k_gain, float eps,
                              const float* __restrict__ rope, int rot, int interleaved,
                              const int* __restrict__ slots, T* __restrict__ k_cache,
-                             T* __restrict__ v_cache, int page_size) {
+                             T* __restrict__ v_cache, int page_size,
+                             const int* __restrict__ positions, float temp_coef, int temp_every) {
     __shared__ float scratch[33];
     pdl_wait();
     const int t = blockIdx.x;
@@ -772,7 +782,8 @@ qk_rownorm_rope_cache_kernel(T* __restrict__ q, long long q_stride, const T* __r
         }
         sk = block_sum(sk, scratch);
     }
-    const float rq = q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f;
+    const float rq = (q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f) *
+                     query_temperature(positions, t, temp_coef, temp_every);
     const float rk = k_gain ? rsqrtf(sk / (float)kw + eps) : 1.f;
     const int slot = slots ? slots[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
@@ -831,7 +842,8 @@ qk_rownorm_rope_cache_bf16x8_kernel(bf16* __restrict__ q, long long q_stride, co
                                     int Hkv, int dk, int dv, const float* __restrict__ q_gain,
                                     const float* __restrict__ k_gain, float eps, const float* __restrict__ rope,
                                     int rot, int interleaved, const int* __restrict__ slots,
-                                    bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int page_size) {
+                                    bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int page_size,
+                                    const int* __restrict__ positions, float temp_coef, int temp_every) {
     extern __shared__ __align__(16) float row_f[];
     __shared__ float scratch[33];
     pdl_wait();
@@ -863,7 +875,8 @@ qk_rownorm_rope_cache_bf16x8_kernel(bf16* __restrict__ q, long long q_stride, co
     }
     sq = block_sum(sq, scratch);
     if (kr) sk = block_sum(sk, scratch);
-    const float rq = q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f;
+    const float rq = (q_gain ? rsqrtf(sq / (float)qw + eps) : 1.f) *
+                     query_temperature(positions, t, temp_coef, temp_every);
     const float rk = (k_gain && kr) ? rsqrtf(sk / (float)kw + eps) : 1.f;
     const int slot = slots ? slots[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
@@ -920,7 +933,8 @@ TGO_API int tgo_qk_rownorm_rope_cache(void* q, long long q_stride, const void* k
                                       int Hkv, int dk, int dv, const float* q_gain,
                                       const float* k_gain, float eps, const float* rope, int rot,
                                       int interleaved, const int* slots, void* k_cache,
-                                      void* v_cache, int page_size, cudaStream_t stream) {
+                                      void* v_cache, int page_size, const int* positions,
+                                      float temp_coef, int temp_every, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dk <= 0 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || H <= 0) return TGO_E_BAD_ARG;
     if ((k || v) && (Hkv <= 0 || page_size <= 0 || !slots || !k_cache)) return TGO_E_BAD_ARG;
@@ -936,17 +950,190 @@ TGO_API int tgo_qk_rownorm_rope_cache(void* q, long long q_stride, const void* k
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
         return tgo_launch_pdl(kern, dim3(T), dim3(256), row_bytes, stream, (bf16*)q, q_stride, (const bf16*)k,
                               k_stride, (const bf16*)v, v_stride, H, Hkv, dk, dv, q_gain, k_gain, eps, rope, rot,
-                              interleaved, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+                              interleaved, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, positions, temp_coef,
+                              temp_every);
     }
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(qk_rownorm_rope_cache_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)q,
                               q_stride, (const bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dk, dv,
                               q_gain, k_gain, eps, rope, rot, interleaved, slots, (bf16*)k_cache,
-                              (bf16*)v_cache, page_size);
+                              (bf16*)v_cache, page_size, positions, temp_coef, temp_every);
     if (dtype == TGO_F32)
         return tgo_launch_pdl(qk_rownorm_rope_cache_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)q,
                               q_stride, (const float*)k, k_stride, (const float*)v, v_stride, H, Hkv, dk,
                               dv, q_gain, k_gain, eps, rope, rot, interleaved, slots, (float*)k_cache,
-                              (float*)v_cache, page_size);
+                              (float*)v_cache, page_size, positions, temp_coef, temp_every);
+    return TGO_E_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------
+// Projection rows of an attention whose q, k and v each pass a short causal convolution over
+// time (per channel, no bias, no activation) before anything else, and whose q and k heads are
+// divided by their root mean square AFTER the rotation (a norm without a gain). Per head
+// vector (a warp each):
+//   c_t   = sum_j w[ch][j] u_(t - taps + 1 + j)[ch]      u: the raw projection rows; rows
+//           before the step's first token of the request come from its kept rows (float32
+//           [taps - 1][C], oldest first, at conv_offset of its state row), zeros before its start
+//   q, k: the first `rot` channels rotated by the token's cosines and sines (either pairing),
+//         then, with `unit_norm`, x / sqrt(mean x^2 + eps) over the head
+//   q goes to q_out [T, H dk]; k to the key plane [page][kv head][offset][dk]; v to the value
+//   plane [page][kv head][offset][dv] at `slots`.
+// C = H dk + Hkv dk + Hkv dv channels, in that order, is also the column order of `qkv` and of
+// the rows of `conv_w` [C, taps]. taps <= 1 with conv_w null: no convolution. Sums, rotation
+// and norm are float32. The kept rows are moved on by a second kernel after this one.
+#define QCR_WARPS 4
+template <typename T>
+__global__ void __launch_bounds__(QCR_WARPS * 32)
+qkv_conv_rope_norm_cache_kernel(
+    const T* __restrict__ qkv, long long qkv_stride, T* __restrict__ q_out, long long q_stride,
+    int H, int Hkv, int dk, int dv, const float* __restrict__ conv_w, int taps,
+    const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+    const int* __restrict__ state_slots, const float* __restrict__ state, long long state_stride,
+    long long conv_offset, const float* __restrict__ rope, int rot, int interleaved, int unit_norm,
+    float eps, const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    int page_size) {
+    extern __shared__ float smem[];
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hh = blockIdx.y * QCR_WARPS + warp;
+    if (hh >= H + 2 * Hkv) return;
+    const int qw = H * dk, kw = Hkv * dk;
+    const int C = qw + kw + Hkv * dv;
+    const bool is_q = hh < H, is_k = !is_q && hh < H + Hkv;
+    const int head = is_q ? hh : is_k ? hh - H : hh - H - Hkv;
+    const int width = (is_q || is_k) ? dk : dv;
+    const int c0 = is_q ? head * dk : is_k ? qw + head * dk : qw + kw + head * dv;
+    const int slot = slots ? slots[t] : -1;
+    if (!is_q && slot < 0) return;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    const int wmax = dk > dv ? dk : dv;
+    float* buf = smem + (size_t)warp * 2 * wmax;
+    float* rotd = buf + wmax;
+    const T* row = qkv + (size_t)t * qkv_stride;
+    if (conv_w && taps > 1) {
+        const int b = seq_ids[t];
+        const int r = t - q_start[b];
+        const float* kept = state + (size_t)state_slots[b] * state_stride + conv_offset;
+        for (int i = lane; i < width; i += 32) {
+            const int c = c0 + i;
+            float a = 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j;
+                const float u = back <= r ? to_f32(*(row - (size_t)back * qkv_stride + c))
+                                          : kept[(size_t)(taps - 1 - (back - r)) * C + c];
+                a = fmaf(conv_w[(size_t)c * taps + j], u, a);
+            }
+            buf[i] = a;
+        }
+    } else {
+        for (int i = lane; i < width; i += 32)
+            buf[i] = to_f32(row[c0 + i]) * (conv_w ? conv_w[c0 + i] : 1.f);
+    }
+    __syncwarp();
+    if (!is_q && !is_k) {
+        T* dst = v_cache + (((size_t)page * Hkv + head) * page_size + off) * dv;
+        for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(buf[i]);
+        return;
+    }
+    const int half = rot / 2;
+    const float* cs = rope ? rope + (size_t)t * rot : nullptr;   // [half] cos, [half] sin
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) {
+        float y = buf[i];
+        if (cs && i < rot) {
+            if (interleaved) {
+                const int pr = i >> 1;
+                y = (i & 1) ? buf[i] * cs[pr] + buf[i - 1] * cs[half + pr]
+                            : buf[i] * cs[pr] - buf[i + 1] * cs[half + pr];
+            } else {
+                y = i < half ? buf[i] * cs[i] - buf[i + half] * cs[half + i]
+                             : buf[i] * cs[i - half] + buf[i - half] * cs[i];
+            }
+        }
+        rotd[i] = y;
+        ss += y * y;
+    }
+    float r = 1.f;
+    if (unit_norm) r = rsqrtf(warp_sum(ss) / (float)dk + eps);
+    T* dst = is_q ? q_out + (size_t)t * q_stride + (size_t)head * dk
+                  : k_cache + (((size_t)page * Hkv + head) * page_size + off) * dk;
+    for (int i = lane; i < dk; i += 32) dst[i] = from_f32<T>(rotd[i] * r);
+}
+
+TGO_API int tgo_qkv_conv_rope_norm_cache(const void* qkv, long long qkv_stride, void* q_out,
+                                         long long q_stride, int dtype, int T, int H, int Hkv, int dk,
+                                         int dv, const float* conv_w, int taps, const int* seq_ids,
+                                         const int* q_start, const int* state_slots,
+                                         const float* state, long long state_stride,
+                                         long long conv_offset, const float* rope, int rot,
+                                         int interleaved, int unit_norm, float eps, const int* slots,
+                                         void* k_cache, void* v_cache, int page_size,
+                                         cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dk <= 0 || dk > 2048 || dv <= 0 || dv > 2048 || rot < 0 || rot > dk || (rot & 1) || H <= 0 ||
+        Hkv <= 0 || page_size <= 0 || !slots || !k_cache || !v_cache || taps < 0 || taps > 64)
+        return TGO_E_BAD_ARG;
+    if (conv_w && taps > 1 &&
+        (!seq_ids || !q_start || !state_slots || !state ||
+         state_stride < conv_offset + (long long)(taps - 1) * ((long long)H * dk + (long long)Hkv * (dk + dv))))
+        return TGO_E_BAD_ARG;
+    const dim3 grid(T, (H + 2 * Hkv + QCR_WARPS - 1) / QCR_WARPS);
+    const size_t smem = (size_t)QCR_WARPS * 2 * (dk > dv ? dk : dv) * sizeof(float);
+    if (dtype == TGO_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(qkv_conv_rope_norm_cache_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(qkv_conv_rope_norm_cache_kernel<bf16>, grid, dim3(QCR_WARPS * 32), smem, stream,
+                              (const bf16*)qkv, qkv_stride, (bf16*)q_out, q_stride, H, Hkv, dk, dv, conv_w, taps,
+                              seq_ids, q_start, state_slots, state, state_stride, conv_offset, rope, rot,
+                              interleaved, unit_norm, eps, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+    }
+    if (dtype == TGO_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(qkv_conv_rope_norm_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(qkv_conv_rope_norm_cache_kernel<float>, grid, dim3(QCR_WARPS * 32), smem, stream,
+                              (const float*)qkv, qkv_stride, (float*)q_out, q_stride, H, Hkv, dk, dv, conv_w,
+                              taps, seq_ids, q_start, state_slots, state, state_stride, conv_offset, rope, rot,
+                              interleaved, unit_norm, eps, slots, (float*)k_cache, (float*)v_cache, page_size);
+    }
+    return TGO_E_BAD_ARG;
+}
+
+// After the convolution over a step's projection rows has run: every request's kept rows
+// become the last taps - 1 of (kept rows, then the step's rows). A thread per (request,
+// channel); x is the [T, C] view the convolution read.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_keep_rows_kernel(const T* __restrict__ x, long long x_stride, int C, int taps,
+                      const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                      float* __restrict__ state, long long state_stride, long long conv_offset) {
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int t0 = q_start[b], n = q_start[b + 1] - t0;
+    float* kept = state + (size_t)state_slots[b] * state_stride + conv_offset;
+    const int keep = taps - 1;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        // ascending i reads kept[n + i] before any later write could reach it (n + i >= i)
+        for (int i = 0; i < keep; ++i) {
+            const int at = n + i;                        // place in (kept, then new)
+            const float v = at < keep ? kept[(size_t)at * C + c]
+                                      : to_f32(x[(size_t)(t0 + at - keep) * x_stride + c]);
+            kept[(size_t)i * C + c] = v;
+        }
+    }
+}
+
+TGO_API int tgo_conv_keep_rows(const void* x, long long x_stride, int dtype, int B, int C, int taps,
+                               const int* q_start, const int* state_slots, float* state,
+                               long long state_stride, long long conv_offset, cudaStream_t stream) {
+    if (B <= 0 || taps <= 1) return 0;
+    if (C <= 0 || taps > 64 || state_stride < conv_offset + (long long)(taps - 1) * C) return TGO_E_BAD_ARG;
+    const int cy = (C + 255) / 256 > 64 ? 64 : (C + 255) / 256;
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(conv_keep_rows_kernel<bf16>, dim3(B, cy), dim3(256), 0, stream, (const bf16*)x,
+                              x_stride, C, taps, q_start, state_slots, state, state_stride, conv_offset);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(conv_keep_rows_kernel<float>, dim3(B, cy), dim3(256), 0, stream, (const float*)x,
+                              x_stride, C, taps, q_start, state_slots, state, state_stride, conv_offset);
     return TGO_E_BAD_ARG;
 }

@@ -88,6 +88,7 @@ struct Request {
 
 struct Manager {
     std::vector<int> kind, window;
+    std::vector<int> keep;           // window groups: the first tokens of a request whose pages stay
     int page_size = 1;
     std::vector<Pool> pools;
     int num_slots = 0;
@@ -116,7 +117,11 @@ struct Manager {
             for (long long i = (long long)t.size(); i < last; ++i) out.push_back((int)i);
             return;
         }
-        const long long first = first_live(g, r.length) / page_size;
+        // the pages of the kept first tokens, then those from the first live position on
+        const long long kept = std::min<long long>(pages_for(keep[g]), last);
+        for (long long i = 0; i < kept; ++i)
+            if (i >= (long long)t.size() || t[i] == NULL_PAGE) out.push_back((int)i);
+        const long long first = std::max<long long>(first_live(g, r.length) / page_size, kept);
         for (long long i = first; i < last; ++i)
             if (i >= (long long)t.size() || t[i] == NULL_PAGE) out.push_back((int)i);
     }
@@ -166,6 +171,7 @@ TGO_HOST_API void* tgo_cache_create(int n_groups, const int* kinds, const int* w
     Manager* m = new Manager();
     m->kind.assign(kinds, kinds + n_groups);
     m->window.assign(windows, windows + n_groups);
+    m->keep.assign(n_groups, 0);
     m->page_size = page_size;
     m->pools.resize(n_groups);
     for (int g = 0; g < n_groups; ++g) {
@@ -177,6 +183,17 @@ TGO_HOST_API void* tgo_cache_create(int n_groups, const int* kinds, const int* w
     for (int i = 0; i < num_slots; ++i) m->free_slots[i] = num_slots - 1 - i;
     m->slot_held.assign(num_slots, 0);
     return m;
+}
+
+// A window group keeps the pages of a request's first keep_first tokens for as long as the
+// request lives (queries read them beside the window). Set before any request is admitted.
+TGO_HOST_API int tgo_cache_set_keep_first(void* p, int group, int keep_first) {
+    Manager* m = M(p);
+    if (group < 0 || group >= (int)m->kind.size() || keep_first < 0 || m->kind[group] != KIND_WINDOW ||
+        !m->requests.empty())
+        return m->fail(BAD_ARGUMENT, "cache: kept first tokens belong to a window group without requests");
+    m->keep[group] = keep_first;
+    return OK;
 }
 
 TGO_HOST_API void tgo_cache_destroy(void* p) { delete M(p); }
@@ -242,7 +259,7 @@ TGO_HOST_API int tgo_cache_commit(void* p, long long handle, long long new_lengt
         const long long dead = m->first_live(g, new_length) / m->page_size;
         std::vector<int>& t = r.tables[g];
         gone.clear();
-        for (long long i = 0; i < std::min<long long>(dead, (long long)t.size()); ++i)
+        for (long long i = m->pages_for(m->keep[g]); i < std::min<long long>(dead, (long long)t.size()); ++i)
             if (t[i] != NULL_PAGE) { gone.push_back(t[i]); t[i] = NULL_PAGE; }
         if (gone.empty()) continue;
         for (int pg : gone) {
@@ -337,7 +354,7 @@ TGO_HOST_API int tgo_cache_can_hold(void* p, long long n_tokens, long long step_
     for (int g = 0; g < (int)m->kind.size(); ++g) {
         long long need = m->pages_for(n_tokens);
         if (m->kind[g] == KIND_WINDOW)
-            need = std::min(need, m->pages_for(m->window[g] - 1 + step_tokens) + 1);
+            need = std::min(need, m->pages_for(m->window[g] - 1 + step_tokens) + 1 + m->pages_for(m->keep[g]));
         if (need > m->pools[g].num_pages) return 0;
     }
     return 1;

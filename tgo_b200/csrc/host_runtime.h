@@ -27,6 +27,8 @@ enum tgo_host_code {
 /* kinds[g]: 0 the group keeps every key, 1 a window of windows[g] keys. NULL on bad sizes. */
 void* tgo_cache_create(int n_groups, const int* kinds, const int* windows, int page_size,
                        const int* pages_per_group, int num_slots);
+/* A window group keeps the pages of a request's first keep_first tokens while it lives. */
+int tgo_cache_set_keep_first(void* cache, int group, int keep_first);
 void tgo_cache_destroy(void* cache);
 const char* tgo_cache_last_error(void* cache, long long info[3]);
 

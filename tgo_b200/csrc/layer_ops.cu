@@ -588,3 +588,178 @@ TGO_API int tgo_add_bias(void* y, int dtype, const float* bias, int T, int d, cu
         return tgo_launch_pdl(add_bias_kernel<float>, grid, block, 0, stream, (float*)y, bias, d, n);
     return TGO_E_BAD_ARG;
 }
+
+// ------------------------------------------------------------ several residual streams
+// A layer arrangement that keeps S copies of the residual stream (x [S, T, d], float32) and
+// learns how a sublayer reads them and writes back:
+//   read    u = sum_s cin[s] x_s;  out = gain * rmsnorm(u)               (the sublayer's input)
+//   write   x_t <- sum_s mix[s][t] x_s + cout[t] * y                      (all t from the old x)
+// The write may also make the next sublayer's input from the new streams (next_in, next_gain:
+// the row is kept in shared memory between the sum of squares and the output), and the plain
+// sum of the new streams (sum_out). A block a token; everything float32 but y and out.
+#define HC_MAX_STREAMS 8
+
+__global__ void stream_spread_kernel(const float* __restrict__ h, float* __restrict__ x, size_t n,
+                                     int S) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = h[i];
+    for (int s = 0; s < S; ++s) x[(size_t)s * n + i] = v;
+}
+
+TGO_API int tgo_stream_spread(const float* h, float* x, long long n, int S, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (S <= 0 || S > HC_MAX_STREAMS) return TGO_E_BAD_ARG;
+    return tgo_launch_pdl(stream_spread_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                          h, x, (size_t)n, S);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+stream_read_norm_kernel(const float* __restrict__ x, int S, int T, int d,
+                        const float* __restrict__ cin, const float* __restrict__ gain, float eps,
+                        TO* __restrict__ out) {
+    extern __shared__ float row[];             // [d]
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t t = blockIdx.x, plane = (size_t)T * d;
+    float c[HC_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s) c[s] = s < S ? cin[s] : 0.f;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) u = fmaf(c[s], x[s * plane + t * d + i], u);
+        row[i] = u;
+        ss += u * u;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        out[t * d + i] = from_f32<TO>((row[i] * r) * gain[i]);
+}
+
+TGO_API int tgo_stream_read_norm(const float* x, int S, int T, int d, const float* cin,
+                                 const float* gain, float eps, void* out, int out_dtype,
+                                 cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (S <= 0 || S > HC_MAX_STREAMS || d <= 0 || d > 24576) return TGO_E_BAD_ARG;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (out_dtype == TGO_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(stream_read_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(stream_read_norm_kernel<bf16>, dim3(T), dim3(256), smem, stream, x, S, T, d,
+                              cin, gain, eps, (bf16*)out);
+    }
+    if (out_dtype != TGO_F32) return TGO_E_BAD_ARG;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(stream_read_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tgo_launch_pdl(stream_read_norm_kernel<float>, dim3(T), dim3(256), smem, stream, x, S, T, d, cin,
+                          gain, eps, (float*)out);
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+stream_write_kernel(float* __restrict__ x, int S, int T, int d, const TY* __restrict__ y,
+                    const float* __restrict__ mix, const float* __restrict__ cout,
+                    const float* __restrict__ next_in, const float* __restrict__ next_gain, float eps,
+                    TO* __restrict__ next_out, float* __restrict__ sum_out) {
+    extern __shared__ float row[];             // [d] when the next input is made here
+    __shared__ float scratch[33];
+    __shared__ float m[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ni[HC_MAX_STREAMS];
+    pdl_wait();
+    if (threadIdx.x < S * S) m[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        co[threadIdx.x] = cout[threadIdx.x];
+        ni[threadIdx.x] = next_in ? next_in[threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    const size_t t = blockIdx.x, plane = (size_t)T * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float old[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) old[s] = x[s * plane + t * d + i];
+        const float yv = to_f32(y[t * d + i]);
+        float u = 0.f, total = 0.f;
+#pragma unroll
+        for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+            if (to >= S) continue;
+            float a = 0.f;
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) a = fmaf(m[s * S + to], old[s], a);
+            a = fmaf(co[to], yv, a);
+            x[to * plane + t * d + i] = a;
+            u = fmaf(ni[to], a, u);
+            total += a;
+        }
+        if (sum_out) sum_out[t * d + i] = total;
+        if (next_out) {
+            row[i] = u;
+            ss += u * u;
+        }
+    }
+    if (!next_out) return;
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        next_out[t * d + i] = from_f32<TO>((row[i] * r) * next_gain[i]);
+}
+
+// y [T, d] in y_dtype; next_out [T, d] in out_dtype (with next_in [S], next_gain [d]) or null;
+// sum_out float32 [T, d] or null.
+TGO_API int tgo_stream_write(float* x, int S, int T, int d, const void* y, int y_dtype,
+                             const float* mix, const float* cout, const float* next_in,
+                             const float* next_gain, float eps, void* next_out, int out_dtype,
+                             float* sum_out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (S <= 0 || S > HC_MAX_STREAMS || d <= 0 || d > 24576) return TGO_E_BAD_ARG;
+    if (next_out && (!next_in || !next_gain)) return TGO_E_BAD_ARG;
+    const size_t smem = next_out ? (size_t)d * sizeof(float) : 0;
+#define HC_GO(TY, TO)                                                                              \
+    do {                                                                                           \
+        if (smem > 48 * 1024)                                                                      \
+            cudaFuncSetAttribute(stream_write_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tgo_launch_pdl(stream_write_kernel<TY, TO>, dim3(T), dim3(256), smem, stream, x, S, T, d, \
+                              (const TY*)y, mix, cout, next_in, next_gain, eps, (TO*)next_out, sum_out); \
+    } while (0)
+    const bool out_bf = next_out && out_dtype == TGO_BF16;
+    if (next_out && out_dtype != TGO_BF16 && out_dtype != TGO_F32) return TGO_E_BAD_ARG;
+    if (y_dtype == TGO_BF16) { if (out_bf) HC_GO(bf16, bf16); else HC_GO(bf16, float); }
+    if (y_dtype == TGO_F32) { if (out_bf) HC_GO(float, bf16); else HC_GO(float, float); }
+#undef HC_GO
+    return TGO_E_BAD_ARG;
+}
+
+// ---------------------------------------------------------------- an activation in place
+// x <- act(x) over [T, f] rows: the hidden rows of a feed-forward without a gate. Codes as in
+// gated_act, and 3: the square of relu.
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ x, size_t n, int act) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float z = to_f32(x[i]);
+    float a;
+    if (act == 1) a = z > 0.f ? z : 0.f;
+    else if (act == 2) a = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else if (act == 3) a = z > 0.f ? z * z : 0.f;
+    else a = z / (1.f + expf(-z));
+    x[i] = from_f32<T>(a);
+}
+
+TGO_API int tgo_act_rows(void* x, int dtype, long long n, int act, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (act < 0 || act > 3) return TGO_E_BAD_ARG;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (dtype == TGO_BF16)
+        return tgo_launch_pdl(act_rows_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)x, (size_t)n, act);
+    if (dtype == TGO_F32)
+        return tgo_launch_pdl(act_rows_kernel<float>, grid, dim3(256), 0, stream, (float*)x, (size_t)n, act);
+    return TGO_E_BAD_ARG;
+}

@@ -93,11 +93,12 @@ class Model:
             need = mixer.cache_need() if hasattr(mixer, "cache_need") else None
             if need is not None:
                 shapes = getattr(need, "plane_shapes", None)
-                key = (need.kind, need.window, need.planes, tuple(need.row_shape), shapes)
+                keep = int(getattr(need, "keep_first", 0) or 0)
+                key = (need.kind, need.window, need.planes, tuple(need.row_shape), shapes, keep)
                 if key not in by_key:
                     by_key[key] = len(self.groups)
                     self.groups.append(GroupLayout(need.kind, need.window, need.planes,
-                                                   need.row_shape, [], shapes))
+                                                   need.row_shape, [], shapes, keep))
                 self.groups[by_key[key]].calls.append(ci)
                 self.call_group[ci] = by_key[key]
             st = mixer.state_need() if hasattr(mixer, "state_need") else None

@@ -163,15 +163,20 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
                       block_tables: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
                       scale: float, window: int, value_dim: Optional[int] = None,
                       sinks: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                      value_row: int = 0) -> None:
+                      value_row: int = 0, keep_first: int = 0,
+                      dist_bias: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention, one warp per (token, head). q is a 2-D view [T, >= H*dh]
     with unit column stride; out likewise. window 0 = every earlier key. `value_dim`: width
     of a value row where it differs from the keys'; `sinks`: float32 [H], a term exp(sink_h)
     in each head's softmax denominator that has no value; `softcap` c > 0: every scaled score
     goes through c tanh(s / c); `value_row`: elements from one value row to the next where
     that is not `value_dim` (values that are the first channels of their key rows: v_cache is
-    k_cache and value_row the key rows' width)."""
-    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks)
+    k_cache and value_row the key rows' width); `keep_first`: with a window, the first keys of
+    a request that every later query still reads; `dist_bias`: float32 [n, H], row
+    min(distance, n - 1) is added to the scaled scores of the keys at that distance."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks, dist_bias)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and
+                                 dist_bias.shape[1] == num_heads and dist_bias.is_contiguous())
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads and
                              sinks.is_contiguous())
     T = q.shape[0]
@@ -186,7 +191,8 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv
         c_int(value_dim or head_dim), _ptr(k_cache),
         _ptr(v_cache), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
         _ptr(seq_ids), _ptr(positions), c_float(scale), c_int(window), _ptr(sinks),
-        c_float(softcap or 0.0), c_int(value_row), _stream()),
+        c_float(softcap or 0.0), c_int(value_row), c_int(keep_first if window else 0),
+        _ptr(dist_bias), c_int(dist_bias.shape[0] if dist_bias is not None else 0), _stream()),
         "attention_generic", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
 
 
@@ -242,6 +248,8 @@ def softcap(x: torch.Tensor, cap: float) -> None:
 
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+# activations of a feed-forward without a gate (and of routed experts): those, and relu squared
+PLAIN_ACTIVATIONS = dict(ACTIVATIONS, relu_squared=3)
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool, activation: str,
@@ -529,13 +537,18 @@ def qk_rownorm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optiona
                           q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
                           rope: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
                           slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
-                          v_cache: Optional[torch.Tensor], page_size: int) -> None:
+                          v_cache: Optional[torch.Tensor], page_size: int,
+                          positions: Optional[torch.Tensor] = None, temp_coef: float = 0.0,
+                          temp_every: int = 0) -> None:
     """Projection rows of an attention whose q/k norm takes a token's WHOLE q row (all heads,
     num_heads * key_dim entries, a gain of that size) and whole k row at once: RMS norm in
     float32, then the first `rotary_dim` channels of every head rotated by `rope` (either
     pairing); q written back in place, k and v stored at `slots` of their cache planes
-    [page, kv head, offset, width]. q, k, v are 2-D views with unit column stride."""
-    _need_cuda(q, k, v, q_gain, k_gain, rope, slots, k_cache, v_cache)
+    [page, kv head, offset, width]. q, k, v are 2-D views with unit column stride. With
+    `positions` (int32 [T]) and `temp_every` > 0 the normed q of a token at position p is also
+    multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)."""
+    _need_cuda(q, k, v, q_gain, k_gain, rope, slots, k_cache, v_cache, positions)
+    assert positions is None or (positions.dtype == torch.int32 and positions.numel() == q.shape[0])
     T = q.shape[0]
     for t in (q, k, v):
         if t is not None:
@@ -556,8 +569,124 @@ def qk_rownorm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optiona
         c_int(num_heads), c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), _ptr(q_gain),
         _ptr(k_gain), c_float(eps), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
         c_int(1 if interleaved else 0), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
-        c_int(page_size), _stream()), "qk_rownorm_rope_cache",
+        c_int(page_size), _ptr(positions if temp_every > 0 else None), c_float(temp_coef),
+        c_int(temp_every), _stream()), "qk_rownorm_rope_cache",
         f"(dk={key_dim}, dv={value_dim}, rotary_dim={rotary_dim})")
+
+
+def qkv_conv_rope_norm_cache(qkv: torch.Tensor, q_out: torch.Tensor, num_heads: int,
+                             num_kv_heads: int, key_dim: int, value_dim: int,
+                             conv_w: Optional[torch.Tensor], num_seqs: int, seq_ids: torch.Tensor,
+                             q_start: torch.Tensor, state_slots: torch.Tensor,
+                             state: Optional[torch.Tensor], conv_offset: int,
+                             rope: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+                             unit_norm: bool, eps: float, slots: torch.Tensor, k_cache: torch.Tensor,
+                             v_cache: torch.Tensor, page_size: int) -> None:
+    """Projection rows [T, H dk + Hkv dk + Hkv dv] (q, k, v side by side) of an attention whose
+    q, k and v each pass a short causal convolution over time (conv_w float32 [C, taps], the
+    last column meets the current token; rows before a request's portion come from its state
+    row, float32 [slots, n] with the last taps - 1 rows [taps - 1, C] at `conv_offset`, which
+    is then moved on), then the first `rotary_dim` channels of q and k rotated by `rope`, then,
+    `unit_norm`, every q and k head divided by sqrt(mean of its squares + eps). q goes to
+    q_out [T, H dk]; k and v to `slots` of their cache planes [page, kv head, offset, width]."""
+    _need_cuda(qkv, q_out, conv_w, seq_ids, q_start, state_slots, state, rope, slots, k_cache, v_cache)
+    T = qkv.shape[0]
+    C = num_heads * key_dim + num_kv_heads * (key_dim + value_dim)
+    assert qkv.shape == (T, C) and qkv.stride(1) == 1 and q_out.stride(1) == 1
+    assert q_out.shape == (T, num_heads * key_dim) and q_out.dtype == qkv.dtype
+    assert k_cache.dtype == qkv.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert slots.dtype == torch.int32 and slots.numel() == T
+    taps = 0
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == C
+        assert seq_ids.dtype == q_start.dtype == state_slots.dtype == torch.int32
+        assert q_start.numel() == num_seqs + 1 and state_slots.numel() == num_seqs
+        if taps > 1:
+            assert state is not None and state.dtype == torch.float32 and state.dim() == 2 and \
+                state.stride(1) == 1
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim) and rope.is_contiguous()
+    lib = load_library("elementwise")
+    has_state = taps > 1
+    _check(lib.tgo_qkv_conv_rope_norm_cache(
+        _ptr(qkv), c_ll(qkv.stride(0)), _ptr(q_out), c_ll(q_out.stride(0)),
+        c_int(dtype_code(qkv.dtype)), c_int(T), c_int(num_heads), c_int(num_kv_heads),
+        c_int(key_dim), c_int(value_dim), _ptr(conv_w), c_int(taps), _ptr(seq_ids), _ptr(q_start),
+        _ptr(state_slots), _ptr(state if has_state else None),
+        c_ll(state.stride(0) if has_state else 0), c_ll(conv_offset), _ptr(rope),
+        c_int(rotary_dim if rope is not None else 0), c_int(1 if interleaved else 0),
+        c_int(1 if unit_norm else 0), c_float(eps), _ptr(slots), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _stream()), "qkv_conv_rope_norm_cache",
+        f"(dk={key_dim}, dv={value_dim}, taps={taps}, rotary_dim={rotary_dim})")
+    if has_state:
+        _check(lib.tgo_conv_keep_rows(
+            _ptr(qkv), c_ll(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), c_int(num_seqs), c_int(C),
+            c_int(taps), _ptr(q_start), _ptr(state_slots), _ptr(state), c_ll(state.stride(0)),
+            c_ll(conv_offset), _stream()), "conv_keep_rows", f"(C={C}, taps={taps})")
+
+
+MAX_STREAMS = 8          # residual streams a layer arrangement may keep (kernels' register budget)
+
+
+def stream_spread(h: torch.Tensor, x: torch.Tensor) -> None:
+    """x[s] = h for every stream s: x float32 [S, T, d], h float32 [T, d]."""
+    _need_cuda(h, x)
+    assert h.dtype == x.dtype == torch.float32 and h.is_contiguous() and x.is_contiguous()
+    assert x.shape[1:] == h.shape
+    lib = load_library("layer_ops")
+    _check(lib.tgo_stream_spread(_ptr(h), _ptr(x), c_ll(h.numel()), c_int(x.shape[0]), _stream()),
+           "stream_spread", f"(streams={x.shape[0]})")
+
+
+def stream_read_norm(x: torch.Tensor, cin: torch.Tensor, gain: torch.Tensor, eps: float,
+                     out: torch.Tensor) -> None:
+    """out = gain * rmsnorm(sum_s cin[s] x[s]): what a sublayer reads of S residual streams
+    (x float32 [S, T, d]; cin float32 [S]; out [T, d] in the activation type)."""
+    _need_cuda(x, cin, gain, out)
+    S, T, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == (T, d)
+    assert cin.dtype == gain.dtype == torch.float32 and cin.numel() == S and gain.numel() == d
+    lib = load_library("layer_ops")
+    _check(lib.tgo_stream_read_norm(_ptr(x), c_int(S), c_int(T), c_int(d), _ptr(cin), _ptr(gain),
+                                    c_float(eps), _ptr(out), c_int(dtype_code(out.dtype)), _stream()),
+           "stream_read_norm", f"(streams={S}, d={d})")
+
+
+def stream_write(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, cout: torch.Tensor,
+                 eps: float = 0.0, next_in: Optional[torch.Tensor] = None,
+                 next_gain: Optional[torch.Tensor] = None, next_out: Optional[torch.Tensor] = None,
+                 sum_out: Optional[torch.Tensor] = None) -> None:
+    """x[t] <- sum_s mix[s, t] x[s] + cout[t] * y for all streams t at once (x float32 [S, T, d],
+    y [T, d], mix float32 [S, S] indexed [from, to], cout float32 [S]). With `next_out` the
+    next sublayer's input gain * rmsnorm(sum_t next_in[t] x[t]) is made from the new streams in
+    the same pass; with `sum_out` (float32 [T, d]) their plain sum."""
+    _need_cuda(x, y, mix, cout, next_in, next_gain, next_out, sum_out)
+    S, T, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == (T, d)
+    assert mix.dtype == cout.dtype == torch.float32 and mix.numel() == S * S and mix.is_contiguous()
+    assert cout.numel() == S
+    if next_out is not None:
+        assert next_out.shape == (T, d) and next_out.is_contiguous()
+        assert next_in.dtype == next_gain.dtype == torch.float32
+        assert next_in.numel() == S and next_gain.numel() == d
+    assert sum_out is None or (sum_out.dtype == torch.float32 and sum_out.shape == (T, d) and
+                               sum_out.is_contiguous())
+    lib = load_library("layer_ops")
+    _check(lib.tgo_stream_write(
+        _ptr(x), c_int(S), c_int(T), c_int(d), _ptr(y), c_int(dtype_code(y.dtype)), _ptr(mix),
+        _ptr(cout), _ptr(next_in), _ptr(next_gain), c_float(eps), _ptr(next_out),
+        c_int(dtype_code(next_out.dtype) if next_out is not None else 0), _ptr(sum_out), _stream()),
+        "stream_write", f"(streams={S}, d={d})")
+
+
+def act_rows(x: torch.Tensor, activation: str) -> None:
+    """x <- activation(x) in place: the hidden rows of a feed-forward without a gate."""
+    _need_cuda(x)
+    assert x.is_contiguous()
+    lib = load_library("layer_ops")
+    _check(lib.tgo_act_rows(_ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.numel()),
+                            c_int(PLAIN_ACTIVATIONS[activation]), _stream()), "act_rows", activation)
 
 
 def mlstm_state_floats(num_heads: int, key_dim: int, value_dim: int) -> int:
@@ -787,24 +916,38 @@ def moe_tile_rows() -> int:
 
 
 def moe_feed_forward(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor],
-                     w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int,
-                     activation: str, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     w_gate: Optional[torch.Tensor], w_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                     activation: str, extra: Optional[torch.Tensor] = None,
+                     scores: str = "chosen", correction: Optional[torch.Tensor] = None,
+                     identity: int = 0, extra_gated: bool = False) -> torch.Tensor:
     """A routed feed-forward: each row of x [T, d] goes to the `top` experts with the largest
-    router logits (w_router float32 [E, d], b_router float32 [E]; float32 sums), weighted by
-    the softmax over those logits alone; expert e is w_down[e] (act(w_gate[e] x) * (w_up[e] x)).
+    router scores (w_router float32 [E, d], b_router float32 [E]; float32 sums); expert e is
+    w_down[e] (act(w_gate[e] x) * (w_up[e] x)), or, with w_gate None, w_down[e] act(w_up[e] x).
     w_gate, w_up [E, ff, d], w_down [E, d, ff] in x's type. `extra` float32 [T, d] is added (a shared
-    expert's output). Returns float32 [T, d]. Nothing is read back to the host."""
-    _need_cuda(x, w_router, b_router, w_gate, w_up, w_down, extra)
+    expert's output). Returns float32 [T, d]. Nothing is read back to the host.
+
+    `scores` "chosen": the choice is by the logits, the weights are the softmax over the chosen
+    logits alone. "all": the scores are the softmax over every logit; the choice is by score +
+    `correction` (float32, one per router output), the weights are the chosen scores divided by
+    their sum. `identity`: the router has that many outputs after the E experts that stand for
+    experts whose output is the row of x itself. `extra_gated`: w_router carries one more row,
+    after all of those, whose logit through a logistic function multiplies `extra`."""
+    _need_cuda(x, w_router, b_router, w_gate, w_up, w_down, extra, correction)
     T, d = x.shape
-    E, ff = w_gate.shape[0], w_gate.shape[1]
-    assert x.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.shape == (E, d)
-    assert w_router.is_contiguous()
-    assert b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == E)
-    assert w_gate.shape == w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff)
+    E, ff = w_up.shape[0], w_up.shape[1]
+    outputs = E + identity
+    assert x.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
+    assert w_router.shape == (outputs + (1 if extra_gated else 0), d)
+    assert b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == outputs)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == outputs)
+    assert w_up.shape == (E, ff, d) and w_down.shape == (E, d, ff)
+    assert w_gate is None or w_gate.shape == w_up.shape
     for w in (w_gate, w_up, w_down):
-        assert w.dtype == x.dtype and w.is_contiguous()
+        assert w is None or (w.dtype == x.dtype and w.is_contiguous())
     assert extra is None or (extra.shape == (T, d) and extra.is_contiguous() and
                              extra.dtype == torch.float32)
+    assert not extra_gated or extra is not None
+    assert 0 < top <= outputs and E > 0 and scores in ("chosen", "all")
     dev, pairs = x.device, T * top
     max_tiles = min(pairs, pairs // moe_tile_rows() + E)
     ints = torch.empty(3 * pairs + 3 * E + 2 + 3 * max_tiles, dtype=torch.int32, device=dev)
@@ -814,20 +957,23 @@ def moe_feed_forward(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional
     tile_info = ints[o + 3 * E + 1:o + 3 * E + 2]
     tiles = ints[o + 3 * E + 2:]
     wts = torch.empty(pairs, dtype=torch.float32, device=dev)
+    gate = torch.empty(T, dtype=torch.float32, device=dev) if extra_gated else None
     hidden = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
     y = torch.empty((pairs, d), dtype=torch.float32, device=dev)
     out = torch.empty((T, d), dtype=torch.float32, device=dev)
     lib = load_library("moe")
     _check(lib.tgo_moe_route(
         _ptr(x), c_ll(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(w_router), _ptr(b_router),
-        c_int(T), c_int(d), c_int(E), c_int(top), _ptr(ids), _ptr(wts), _ptr(counts), _ptr(fill),
+        c_int(T), c_int(d), c_int(outputs), c_int(top), _ptr(ids), _ptr(wts), _ptr(counts), _ptr(fill),
         _ptr(offsets), _ptr(perm), _ptr(place), _ptr(tile_info), _ptr(tiles), c_int(max_tiles),
-        _stream()), "moe_route", f"(E={E}, top={top})")
+        c_int(1 if scores == "all" else 0), _ptr(correction), c_int(E), _ptr(gate),
+        _stream()), "moe_route", f"(E={E}+{identity}, top={top})")
     _check(lib.tgo_moe_experts(
         _ptr(x), c_ll(x.stride(0)), c_int(dtype_code(x.dtype)), _ptr(w_gate), _ptr(w_up),
         _ptr(w_down), _ptr(hidden), _ptr(y), _ptr(wts), _ptr(extra), _ptr(out), c_int(T), c_int(d),
-        c_int(ff), c_int(top), c_int(ACTIVATIONS[activation]), _ptr(perm), _ptr(tile_info),
-        _ptr(tiles), c_int(max_tiles), _stream()), "moe_experts", f"(d={d}, ff={ff})")
+        c_int(ff), c_int(top), c_int(PLAIN_ACTIVATIONS[activation]), _ptr(perm), _ptr(tile_info),
+        _ptr(tiles), c_int(max_tiles), _ptr(ids if identity else None), c_int(E), _ptr(gate),
+        _stream()), "moe_experts", f"(d={d}, ff={ff})")
     LAUNCHES[0] += 4
     return out
 

@@ -10,14 +10,24 @@
     and enters unscaled, a single time;
   - `qk_norm` with scope "row": q and k are RMS-normed over a token's whole projection row
     (all heads at once, gains as wide as the rows), before the heads are split and rotated;
-  - `softcap` c: every scaled score goes through c tanh(score / c) before the softmax.
+  - `softcap` c: every scaled score goes through c tanh(score / c) before the softmax;
+  - `conv_taps`: q, k and v each pass a causal convolution of that many taps over time (per
+    channel, no bias), straight after their projections; the last taps - 1 projected rows of
+    a request are its state;
+  - `qk_unit_norm`: every q and k head is divided by its root mean square after the rotation;
+  - `keep_first`: beside the window a query reads the first keep_first keys of its request;
+  - `query_temperature` (coef, every): q at position p times 1 + coef ln(floor((p+1)/every) + 1);
+  - `distance_bias_max` D: a learned table [rows, heads] adds table[bucket(i - j), h] to the
+    scaled score, bucket(n) = n below rows/2, then min(rows - 1, rows/2 + floor(ln(n / (rows/2))
+    / ln(D / (rows/2)) * (rows - rows/2))).
 
     score(i, j) = (q_i . k_j) * scale       for 0 <= i - j < window
     w(i, j)     = exp(score(i, j)) / (exp(sink_h) + sum_j' exp(score(i, j')))
     out_i       = Wo concat_h sum_j w_h(i, j) v_kv(h)(j)
 
 Scores, softmax and sums are float32. Tensor roles: q, k, v, o and, with `bias`, q_bias, k_bias,
-v_bias; with `sink`, sink; with the row norm, q_norm, k_norm.
+v_bias; with `sink`, sink; with the row norm, q_norm, k_norm; with the convolution, q_conv,
+k_conv, v_conv ([channels, taps]); with the distance bias, distance_bias.
 """
 from __future__ import annotations
 
@@ -31,7 +41,31 @@ from ..kernels import ops
 from ..registry import MIXERS, POSITIONS
 from ..weights.binder import WeightSpec
 from .attention import decode_splits, step_tiles
-from .base import CacheNeed, LayerCache, Part
+from .base import CacheNeed, LayerCache, Part, StateNeed
+
+
+def distance_bucket(n: int, rows: int, bias_max: int) -> int:
+    """Row of a distance-bias table for the distance n >= 0."""
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half)
+                                               * (rows - half))))
+
+
+def bias_by_distance(table: torch.Tensor, bias_max: int) -> torch.Tensor:
+    """[rows, heads] -> [n, heads] float32 with row i the bias at distance i; the last row
+    stands for every larger distance (from bias_max on the bucket is the last one)."""
+    rows = table.shape[0]
+    if rows < 2 or bias_max <= rows // 2:
+        raise ValueError(f"attention: a distance bias of {rows} rows up to distance {bias_max}; "
+                         "the table needs two rows and a distance beyond its linear half")
+    n = 1
+    while distance_bucket(n - 1, rows, bias_max) < rows - 1:     # ends: bucket(bias_max) is the last
+        n += 1
+    idx = torch.tensor([distance_bucket(i, rows, bias_max) for i in range(n)], dtype=torch.long,
+                       device=table.device)
+    return table.to(torch.float32).index_select(0, idx).contiguous()
 
 
 class SinkAttention(Part):
@@ -59,11 +93,25 @@ class SinkAttention(Part):
         if self.position is not None and not hasattr(self.position, "table"):
             raise ValueError("attention: this mixer rotates inside its own kernel and needs a "
                              "position encoding that offers a table of cosines and sines")
+        self.taps = int(getattr(spec, "conv_taps", 0) or 0)
+        self.unit_norm = bool(getattr(spec, "qk_unit_norm", False))
+        self.keep_first = int(getattr(spec, "keep_first", 0) or 0)
+        if self.keep_first and not self.window:
+            raise ValueError("attention: keep_first belongs to a window")
+        self.temperature = getattr(spec, "query_temperature", None)
+        self.bias_max = getattr(spec, "distance_bias_max", None)
+        if (self.taps or self.unit_norm) and (self.bias or self.row_norm):
+            raise ValueError("attention: the convolution and the unit norm after the rotation are "
+                             "not offered together with biases or the row norm")
+        if self.temperature is not None and not self.row_norm:
+            raise ValueError("attention: the query temperature is applied by the row norm's kernel")
         roles = ["q", "k", "v", "o"] + (["q_bias", "k_bias", "v_bias"] if self.bias else []) + \
-            (["sink"] if self.sink else []) + (["q_norm", "k_norm"] if self.row_norm else [])
+            (["sink"] if self.sink else []) + (["q_norm", "k_norm"] if self.row_norm else []) + \
+            (["q_conv", "k_conv", "v_conv"] if self.taps else []) + \
+            (["distance_bias"] if self.bias_max is not None else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "attention")
         self.w_qkv = self.w_o = self.b_q = self.b_k = self.b_v = self.sinks = None
-        self.q_gain = self.k_gain = None
+        self.q_gain = self.k_gain = self.conv = self.dist_bias = None
 
     def weight_specs(self):
         n, d = self.names, self.hidden
@@ -77,12 +125,22 @@ class SinkAttention(Part):
             out.append(WeightSpec(n["sink"], (self.H,), "gain"))
         if self.row_norm:
             out += [WeightSpec(n["q_norm"], (qw,), "gain"), WeightSpec(n["k_norm"], (kw,), "gain")]
+        if self.taps:
+            out += [WeightSpec(n["q_conv"], (qw, self.taps), "constant"),
+                    WeightSpec(n["k_conv"], (kw, self.taps), "constant"),
+                    WeightSpec(n["v_conv"], (vw, self.taps), "constant")]
+        if self.bias_max is not None:
+            out.append(WeightSpec(n["distance_bias"], (-1, self.H), "constant"))   # rows: the tensor's
         return out
 
     def cache_need(self):
-        return CacheNeed.keys_and_values_of(self.window, self.Hkv, self.dk, self.dv)
+        return CacheNeed.keys_and_values_of(self.window, self.Hkv, self.dk, self.dv,
+                                            keep_first=self.keep_first)
 
     def state_need(self):
+        """The convolution's last taps - 1 projected rows (q, k, v side by side)."""
+        if self.taps > 1:
+            return StateNeed(((self.taps - 1) * (self.H * self.dk + self.Hkv * (self.dk + self.dv)),))
         return None
 
     def bind(self, weights):
@@ -98,6 +156,11 @@ class SinkAttention(Part):
         if self.row_norm:
             self.q_gain = weights.pop(n["q_norm"]).to(torch.float32).contiguous()
             self.k_gain = weights.pop(n["k_norm"]).to(torch.float32).contiguous()
+        if self.taps:
+            self.conv = torch.cat([weights.pop(n[r]).to(torch.float32) for r in
+                                   ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        if self.bias_max is not None:
+            self.dist_bias = bias_by_distance(weights.pop(n["distance_bias"]), int(self.bias_max))
 
     def libraries(self, dtype, page_size) -> List[str]:
         names = ["sgemm" if dtype == torch.float32 else "gemm_skinny", "elementwise",
@@ -137,16 +200,23 @@ class SinkAttention(Part):
         if self.position is not None:
             table, rot = self.position.table(ctx), self.position.rotary_dim
             interleaved = getattr(self.position, "pairing", "half_split") == "interleaved"
-        if self.row_norm:
+        if self.taps or self.unit_norm:
+            q = torch.empty((x.shape[0], qw), dtype=qkv.dtype, device=qkv.device)
+            ops.qkv_conv_rope_norm_cache(qkv, q, H, Hkv, dk, dv, self.conv, ctx.num_seqs, ctx.seq_ids,
+                                         ctx.q_start, ctx.state_slots, cache.state, 0, table, rot,
+                                         interleaved, self.unit_norm, self.eps, cache.slots, cache.k,
+                                         cache.v, cache.page_size)
+        elif self.row_norm:
+            coef, every = self.temperature or (0.0, 0)
             ops.qk_rownorm_rope_cache(q, k, v, H, Hkv, dk, dv, self.q_gain, self.k_gain, self.eps,
                                       table, rot, interleaved, cache.slots, cache.k, cache.v,
-                                      cache.page_size)
+                                      cache.page_size, ctx.positions, float(coef), int(every))
         else:
             ops.qkv_bias_rope_cache(q, k, v, H, Hkv, dk, dv, self.b_q, self.b_k, self.b_v, table,
                                     rot, interleaved, cache.slots, cache.k, cache.v, cache.page_size)
         a = torch.empty((x.shape[0], H * dv), dtype=q.dtype, device=q.device)
         sink_attention(q, a, H, Hkv, dk, dv, cache, ctx, self.scale, self.window or 0, self.sinks,
-                       softcap=self.softcap)
+                       softcap=self.softcap, keep_first=self.keep_first, dist_bias=self.dist_bias)
         return ops.linear(a, self.w_o, out_dtype=self.out_dtype)
 
 
@@ -167,8 +237,9 @@ def tile_form(H, Hkv, dk, dv, value_row, dtype):
 
 
 def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, softcap=0.0,
-                   value_row=0) -> None:
-    """`softcap` bounds the scores; `value_row` > 0 says that a value is the first dv channels
+                   value_row=0, keep_first=0, dist_bias=None) -> None:
+    """`keep_first`: the first keys of a request that stay visible beside the window; `dist_bias`
+    [n, H]: added to the scores by distance. `softcap` bounds the scores; `value_row` > 0 says that a value is the first dv channels
     of its key row, `value_row` wide (one cache plane serves as keys and values).
     Which kernel runs the attention of a step. bfloat16 at sizes a tensor-core kernel takes
     (`tile_form`): that kernel, over tiles of consecutive tokens for steps with prompt portions
@@ -177,6 +248,8 @@ def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, sof
     and other sizes: the generic kernel (a warp per token and head, keys in a fixed order)."""
     v_cache = cache.k if value_row else cache.v
     form, tokens = tile_form(H, Hkv, dk, dv, value_row, q.dtype)
+    if keep_first or dist_bias is not None:
+        form = None                     # the tile kernels know neither
     if form is not None and ops.attention_sink_takes(q, out):
         tok0, ntok = (None, None) if ctx.decode_only else step_tiles(ctx, tokens)
         if form == "wide":
@@ -195,7 +268,8 @@ def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, sof
         return
     ops.attention_generic(q, out, H, Hkv, dk, cache.k, v_cache, cache.page_size,
                           cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
-                          value_dim=dv, sinks=sinks, softcap=softcap, value_row=value_row)
+                          value_dim=dv, sinks=sinks, softcap=softcap, value_row=value_row,
+                          keep_first=keep_first, dist_bias=dist_bias)
 
 
 MIXERS.register("sink_attention", SinkAttention)

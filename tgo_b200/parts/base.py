@@ -68,23 +68,27 @@ class CacheNeed:
     planes: int
     row_shape: Tuple[int, ...]
     plane_shapes: Optional[Tuple[Tuple[int, ...], ...]] = None   # rows that differ by plane
+    keep_first: int = 0           # a window group: the first tokens of a request that stay
 
     @staticmethod
-    def keys_and_values(window: Optional[int], num_kv_heads: int, head_dim: int) -> "CacheNeed":
+    def keys_and_values(window: Optional[int], num_kv_heads: int, head_dim: int,
+                        keep_first: int = 0) -> "CacheNeed":
         kind = "full" if window is None else "window"
         return CacheNeed(kind, None if window is None else int(window), 2,
-                         (int(num_kv_heads), int(head_dim)))
+                         (int(num_kv_heads), int(head_dim)),
+                         keep_first=int(keep_first) if window is not None else 0)
 
     @staticmethod
     def keys_and_values_of(window: Optional[int], num_kv_heads: int, key_dim: int,
-                           value_dim: int) -> "CacheNeed":
+                           value_dim: int, keep_first: int = 0) -> "CacheNeed":
         """Keys of one width and values of another: two planes with rows of their own."""
         if key_dim == value_dim:
-            return CacheNeed.keys_and_values(window, num_kv_heads, key_dim)
+            return CacheNeed.keys_and_values(window, num_kv_heads, key_dim, keep_first)
         kind = "full" if window is None else "window"
         return CacheNeed(kind, None if window is None else int(window), 2,
                          (int(num_kv_heads), int(key_dim)),
-                         ((int(num_kv_heads), int(key_dim)), (int(num_kv_heads), int(value_dim))))
+                         ((int(num_kv_heads), int(key_dim)), (int(num_kv_heads), int(value_dim))),
+                         keep_first=int(keep_first) if window is not None else 0)
 
 
 @dataclass(frozen=True)

@@ -29,6 +29,8 @@ class PreNormResidual(Part):
         self.norm1 = NORMS.get(spec.norm.kind)(spec.norm, hidden, names["mixer_norm"])
         self.norm2 = NORMS.get(spec.norm.kind)(spec.norm, hidden, names["ffn_norm"])
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
+        if spec.feed_forward is None:
+            raise ValueError("pre-norm block: a layer needs a feed-forward")
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
             spec.feed_forward, hidden, p, device)
         # a part whose forward takes `residual` may add its result to the stream itself
@@ -370,3 +372,116 @@ class PostNormResidual(Part):
 
 
 BLOCKS.register("postnorm_residual", PostNormResidual)
+
+
+class HyperConnections(Part):
+    """Arrangement with `streams` copies x_1 .. x_S of the residual stream and learned
+    coefficients for how each sublayer reads them and writes back. For sublayer q (the mixer,
+    then the feed-forward) with coefficients in_q [S], out_q [S] and mix_q [S, S] ([from, to]):
+
+        u   = sum_s in_q[s] x_s
+        y   = sublayer_q(norm_q(u))
+        x_t = sum_s mix_q[s, t] x_s + out_q[t] y          all t at once, from the old streams
+
+    All streams equal the block's input when it is the first of its kind to run; what the
+    block hands on as the stream is the sum of its streams, and the streams themselves stay
+    in the step's context for the next block of this kind. Streams, coefficients, norms and
+    sums are float32. The write of the mixer's result also makes the feed-forward's input.
+    A layer may have no feed-forward. Tensor roles of the layer spec: mixer_norm, mixer_in,
+    mixer_out, mixer_mix and ffn_norm, ffn_in, ffn_out, ffn_mix."""
+
+    STREAMS_KEY = "residual_streams"     # ctx.aux: (the summed stream it belongs to, x [S, T, d])
+
+    def __init__(self, spec: LayerSpec, hidden: int, device=None):
+        p = spec.prefix
+        self.S = int(spec.streams)
+        if not 1 <= self.S <= ops.MAX_STREAMS:
+            raise ValueError(f"hyper-connections block: {self.S} streams; 1 to {ops.MAX_STREAMS}")
+        has_ffn = spec.feed_forward is not None
+        roles = ["mixer_norm", "mixer_in", "mixer_out", "mixer_mix"] + \
+            (["ffn_norm", "ffn_in", "ffn_out", "ffn_mix"] if has_ffn else [])
+        self.names = tensor_names(spec.tensors, p, roles, "hyper-connections block")
+        self.hidden = hidden
+        make = NORMS.get(spec.norm.kind)
+        self.norm1 = make(spec.norm, hidden, self.names["mixer_norm"])
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
+        self.norm2 = self.feed_forward = None
+        if has_ffn:
+            self.norm2 = make(spec.norm, hidden, self.names["ffn_norm"])
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
+                spec.feed_forward, hidden, p, device)
+        for norm in (self.norm1, self.norm2):
+            if norm is not None and (not hasattr(norm, "gain") or getattr(norm, "groups", 1) != 1):
+                raise ValueError(f"hyper-connections block: the norm {spec.norm.kind!r} is not a "
+                                 "plain RMS norm with a gain")
+        # the write into the streams is float32: the sublayers' last products keep float32 rows
+        for part in (self.mixer, self.feed_forward):
+            if part is not None and hasattr(part, "out_dtype"):
+                part.out_dtype = torch.float32
+        self.coef = {}
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def weight_specs(self):
+        out = []
+        for part in self.parts():
+            out += part.weight_specs()
+        S = self.S
+        for q in ("mixer", "ffn") if self.feed_forward is not None else ("mixer",):
+            out += [WeightSpec(self.names[q + "_in"], (S,), "gain"),
+                    WeightSpec(self.names[q + "_out"], (S,), "gain"),
+                    WeightSpec(self.names[q + "_mix"], (S, S), "constant")]
+        return out
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+        for role, name in self.names.items():
+            if role.endswith(("_in", "_out", "_mix")):
+                self.coef[role] = weights[name].to(torch.float32).contiguous()
+
+    def libraries(self, dtype, page_size):
+        out = ["layer_ops"]
+        for part in self.parts():
+            out += offered(part, "libraries")(dtype, page_size)
+        return out
+
+    def prepare_capture(self, ctx, cache):
+        for part in self.parts():
+            offered(part, "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, writes_cache=True):
+        return sum(offered(part, "flops")(extents, first_positions, writes_cache)
+                   for part in self.parts())
+
+    def cache_bytes_read(self, context_len, width):
+        return offered(self.mixer, "cache_bytes_read")(context_len, width)
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None:
+            ops.residual_add(h, pending)
+            ctx.aux.pop(self.STREAMS_KEY, None)
+        got = ctx.aux.get(self.STREAMS_KEY)
+        if got is not None and got[0] is h and got[1].shape[0] == self.S:
+            x = got[1]
+        else:
+            x = torch.empty((self.S,) + tuple(h.shape), dtype=torch.float32, device=h.device)
+            ops.stream_spread(h, x)
+        c, eps = self.coef, self.norm1.eps
+        n = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+        ops.stream_read_norm(x, c["mixer_in"], self.norm1.gain, eps, n)
+        y = self.mixer.forward(n, ctx, cache)
+        if self.feed_forward is None:
+            ops.stream_write(x, y, c["mixer_mix"], c["mixer_out"], sum_out=h)
+        else:
+            n = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+            ops.stream_write(x, y, c["mixer_mix"], c["mixer_out"], self.norm2.eps, c["ffn_in"],
+                             self.norm2.gain, n)
+            y = self.feed_forward.forward(n, ctx)
+            ops.stream_write(x, y, c["ffn_mix"], c["ffn_out"], sum_out=h)
+        ctx.aux[self.STREAMS_KEY] = (h, x)
+        return h, None
+
+
+BLOCKS.register("hyper_connections", HyperConnections)

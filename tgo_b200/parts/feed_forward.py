@@ -115,6 +115,43 @@ FEED_FORWARDS.register("swiglu", SwiGLU)
 FEED_FORWARDS.register("gated_dense", SwiGLU)      # the gate's activation is the spec's
 
 
+class PlainDense(Part):
+    """A feed-forward without a gate: W_down act(W_up x), act one of `ops.PLAIN_ACTIVATIONS`
+    (the spec's `activation`), no biases. Tensor roles: up, down."""
+    out_dtype = None
+
+    def __init__(self, spec: FeedForwardSpec, hidden: int, prefix: str, device=None):
+        self.hidden, self.inter = hidden, spec.intermediate_size
+        self.activation = spec.activation or "silu"
+        if self.activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation {self.activation!r}; known: "
+                             f"{sorted(ops.PLAIN_ACTIVATIONS)}")
+        self.names = tensor_names(spec.tensors, prefix, ["up", "down"], "feed-forward")
+        self.w_up = self.w_down = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.names["up"], (self.inter, self.hidden)),
+                WeightSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def bind(self, weights):
+        self.w_up = weights.pop(self.names["up"]).contiguous()
+        self.w_down = weights.pop(self.names["down"]).contiguous()
+
+    def libraries(self, dtype, page_size) -> List[str]:
+        return ["sgemm" if dtype == torch.float32 else "gemm_skinny", "layer_ops"]
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        return 2.0 * sum(extents) * self.hidden * 2 * self.inter
+
+    def forward(self, x, ctx, residual=None):
+        hidden = ops.linear(ops.rows_of(x), self.w_up)
+        ops.act_rows(hidden, self.activation)
+        return ops.linear(hidden, self.w_down, residual=residual, out_dtype=self.out_dtype)
+
+
+FEED_FORWARDS.register("plain_dense", PlainDense)
+
+
 class RoutedExperts(Part):
     """A routed feed-forward (mixture of experts): `experts` gated feed-forwards without
     biases, of which every token uses the `top` with the largest router logits,
@@ -127,22 +164,42 @@ class RoutedExperts(Part):
     bind time ([E, ff, d] and [E, d, ff]); routing, the products over each expert's tokens and
     the weighted sum run on the device without a word to the host. The spec's `tensors` table
     names expert tensors with a `{e}` in them: roles expert_gate, expert_up, expert_down, router
-    and, with `router_bias`, router_bias. `shared` is a FeedForwardSpec of its own kind."""
+    and, with `router_bias`, router_bias. `shared` is a FeedForwardSpec of its own kind.
+
+    What the spec may change: `gated` False, experts W_down act(W_up x) without a gate matrix
+    (no role expert_gate); `router_scores` "all", the scores are the softmax over every router
+    output, the weights the chosen scores divided by their sum (+ 1e-20), and with
+    `router_correction` (role router_correction) the choice is by score + correction while the
+    weights are not; `identity_experts` n, the router has n more outputs after the experts,
+    whose expert gives back its input; `shared_gate` (role shared_gate, [1, hidden]), the shared
+    feed-forward's output is multiplied by a logistic gate per token (the gate's row rides as
+    the router matrix's last row, so its logit is a float32 sum too)."""
     out_dtype = None        # the result is float32 rows when a block asks, else the activations'
 
     def __init__(self, spec: FeedForwardSpec, hidden: int, prefix: str, device=None):
         self.hidden = hidden
         self.inter = spec.intermediate_size
         self.E, self.top = int(spec.experts), int(spec.top)
-        if not 0 < self.top <= self.E:
-            raise ValueError(f"routed feed-forward: top {self.top} of {self.E} experts")
+        self.gated = bool(getattr(spec, "gated", True))
+        self.identity = int(getattr(spec, "identity_experts", 0) or 0)
+        self.scores = "all" if getattr(spec, "router_scores", "chosen") == "all" else "chosen"
+        self.correction = bool(getattr(spec, "router_correction", False))
+        self.shared_gate = bool(getattr(spec, "shared_gate", False))
+        if not 0 < self.top <= self.E + self.identity:
+            raise ValueError(f"routed feed-forward: top {self.top} of {self.E + self.identity} experts")
+        if self.shared_gate and spec.shared is None:
+            raise ValueError("routed feed-forward: a gate on the shared feed-forward needs one")
+        if self.correction and self.scores != "all":
+            raise ValueError("routed feed-forward: the correction belongs to scores over all experts")
         self.activation = spec.activation or "silu"
-        if self.activation not in ops.ACTIVATIONS:
-            raise ValueError(f"feed-forward: activation {self.activation!r}; known: "
-                             f"{sorted(ops.ACTIVATIONS)}")
+        known = ops.ACTIVATIONS if self.gated else ops.PLAIN_ACTIVATIONS
+        if self.activation not in known:
+            raise ValueError(f"feed-forward: activation {self.activation!r}; known: {sorted(known)}")
         self.router_bias = bool(spec.router_bias)
-        roles = ["expert_gate", "expert_up", "expert_down", "router"] + \
-            (["router_bias"] if self.router_bias else [])
+        roles = (["expert_gate"] if self.gated else []) + ["expert_up", "expert_down", "router"] + \
+            (["router_bias"] if self.router_bias else []) + \
+            (["router_correction"] if self.correction else []) + \
+            (["shared_gate"] if self.shared_gate else [])
         self.names = tensor_names(spec.tensors, prefix, roles, "routed feed-forward")
         self.shared = None
         if spec.shared is not None:
@@ -150,6 +207,7 @@ class RoutedExperts(Part):
             if hasattr(self.shared, "out_dtype"):
                 self.shared.out_dtype = torch.float32       # it joins a float32 sum
         self.w_gate = self.w_up = self.w_down = self.w_router = self.b_router = None
+        self.router_correction = None
 
     def _expert(self, role: str, e: int) -> str:
         return self.names[role].replace("{e}", str(e))
@@ -160,13 +218,19 @@ class RoutedExperts(Part):
     def weight_specs(self):
         f, d = self.inter, self.hidden
         out = []
+        outputs = self.E + self.identity
         for e in range(self.E):
-            out += [WeightSpec(self._expert("expert_gate", e), (f, d)),
-                    WeightSpec(self._expert("expert_up", e), (f, d)),
+            if self.gated:
+                out.append(WeightSpec(self._expert("expert_gate", e), (f, d)))
+            out += [WeightSpec(self._expert("expert_up", e), (f, d)),
                     WeightSpec(self._expert("expert_down", e), (d, f))]
-        out.append(WeightSpec(self.names["router"], (self.E, d), "constant"))
+        out.append(WeightSpec(self.names["router"], (outputs, d), "constant"))
         if self.router_bias:
-            out.append(WeightSpec(self.names["router_bias"], (self.E,), "gain"))
+            out.append(WeightSpec(self.names["router_bias"], (outputs,), "gain"))
+        if self.correction:
+            out.append(WeightSpec(self.names["router_correction"], (outputs,), "gain"))
+        if self.shared_gate:
+            out.append(WeightSpec(self.names["shared_gate"], (1, d), "constant"))
         if self.shared is not None:
             out += self.shared.weight_specs()
         return out
@@ -174,10 +238,17 @@ class RoutedExperts(Part):
     def bind(self, weights):
         stack = lambda role: torch.stack(                                       # noqa: E731
             [weights.pop(self._expert(role, e)) for e in range(self.E)], dim=0).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack("expert_gate"), stack("expert_up"), stack("expert_down")
+        self.w_gate = stack("expert_gate") if self.gated else None
+        self.w_up, self.w_down = stack("expert_up"), stack("expert_down")
         self.w_router = weights.pop(self.names["router"]).to(torch.float32).contiguous()
+        if self.shared_gate:
+            gate_row = weights.pop(self.names["shared_gate"]).to(torch.float32).reshape(1, -1)
+            self.w_router = torch.cat([self.w_router, gate_row], dim=0).contiguous()
         if self.router_bias:
             self.b_router = weights.pop(self.names["router_bias"]).to(torch.float32).contiguous()
+        if self.correction:
+            self.router_correction = weights.pop(self.names["router_correction"]).to(
+                torch.float32).contiguous()
         if self.shared is not None:
             self.shared.bind(weights)
 
@@ -189,7 +260,8 @@ class RoutedExperts(Part):
 
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         n = sum(extents)
-        total = 2.0 * n * self.hidden * self.E + 2.0 * n * self.top * self.hidden * 3 * self.inter
+        total = 2.0 * n * self.hidden * (self.E + self.identity) + \
+            2.0 * n * self.top * self.hidden * (3 if self.gated else 2) * self.inter
         if self.shared is not None:
             total += self.shared.flops(extents, first_positions, writes_cache)
         return total
@@ -198,7 +270,8 @@ class RoutedExperts(Part):
         x = ops.rows_of(x)
         extra = self.shared.forward(x, ctx) if self.shared is not None else None
         y = ops.moe_feed_forward(x, self.w_router, self.b_router, self.w_gate, self.w_up,
-                                 self.w_down, self.top, self.activation, extra)
+                                 self.w_down, self.top, self.activation, extra, self.scores,
+                                 self.router_correction, self.identity, self.shared_gate)
         want = self.out_dtype or ctx.act_dtype
         if want == torch.float32:
             return y

@@ -73,6 +73,9 @@ def _register_builtin() -> None:
     from .config import derosun
     if derosun.ARCHITECTURE not in ARCHITECTURES:
         ARCHITECTURES.register(derosun.ARCHITECTURE, derosun.derosun_model_spec)
+    from .config import vimelorn
+    if vimelorn.ARCHITECTURE not in ARCHITECTURES:
+        ARCHITECTURES.register(vimelorn.ARCHITECTURE, vimelorn.vimelorn_model_spec)
 
 
 _register_builtin()

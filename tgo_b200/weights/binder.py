@@ -36,6 +36,12 @@ class WeightSpec:
                                   # if it is there)
 
 
+def _fits(shape, declared) -> bool:
+    """A declared extent of -1 stands for any positive size: the tensor's own shape gives it."""
+    return len(shape) == len(declared) and all(d == s or (d == -1 and s > 0)
+                                               for s, d in zip(shape, declared))
+
+
 class WeightError(ValueError):
     """The checkpoint does not hold what the model declares."""
 
@@ -71,7 +77,7 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
         if n in have:
             dt, shape = have[n]
             shape, declared = tuple(shape), tuple(want[n].shape)
-            if any(int(s) == 0 for s in shape) and shape != declared:
+            if any(int(s) == 0 for s in shape) and not _fits(shape, declared):
                 # weights/weights.go:605-610: a tensor without elements is a broken file
                 wrong.append(f"{n} is empty (shape {list(shape)})")
             elif want[n].role not in ("other", "constant") and len(shape) not in (1, 2):
@@ -83,7 +89,7 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
                 # model/weights.go:224-234: the field to change is in config.json, so name it
                 wrong.append(f"config: vocab_size is {declared[0]} and {n} has {shape[0]} rows; "
                              "the config and the weights are from different models")
-            elif shape != declared:
+            elif not _fits(shape, declared):
                 wrong.append(f"{n} is {list(shape)}, declared {list(declared)}")
             elif dt not in ("BF16", "F16", "F32") and want[n].role != "other":
                 wrong.append(f"{n} is stored as {dt}; BF16, F16 or F32 is needed")
