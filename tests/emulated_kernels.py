@@ -87,7 +87,7 @@ def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gai
 
 def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cache, page_size,
                       block_tables, seq_ids, positions, scale, window, value_dim=None, sinks=None,
-                      softcap=0.0, value_row=0):
+                      softcap=0.0, value_row=0, keep_first=0, dist_bias=None):
     T = q.shape[0]
     group = num_heads // num_kv_heads
     dv = value_dim or head_dim
@@ -99,6 +99,8 @@ def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cach
             continue
         lo = max(0, p - window + 1) if window > 0 else 0
         idx = torch.arange(lo, p + 1)
+        if window > 0 and keep_first:
+            idx = torch.cat([torch.arange(0, min(keep_first, lo)), idx])
         pages = block_tables[b].long()[idx // page_size]
         offs = idx % page_size
         for h in range(num_heads):
@@ -109,6 +111,8 @@ def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cach
             s = (K @ qv) * scale
             if softcap:
                 s = softcap * torch.tanh(s / softcap)
+            if dist_bias is not None:
+                s = s + dist_bias[torch.clamp(p - idx, max=dist_bias.shape[0] - 1), h]
             if sinks is not None:
                 w = torch.softmax(torch.cat([s, sinks[h:h + 1].float()]), dim=0)[:-1]
             else:
@@ -220,6 +224,8 @@ def attention_mixed(q, out, num_heads, num_kv_heads, key_dim, value_dim, k_cache
             continue
         lo = max(0, p - window + 1) if window > 0 else 0
         idx = torch.arange(lo, p + 1)
+        if window > 0 and keep_first:
+            idx = torch.cat([torch.arange(0, min(keep_first, lo)), idx])
         pages = block_tables[b].long()[idx // page_size]
         offs = idx % page_size
         w = []
@@ -411,24 +417,111 @@ def selective_scan(xbc, dt_raw, dt_bias, a_log, d_skip, y, num_seqs, heads, grou
             y[t] = out.reshape(-1)
 
 
-def moe_feed_forward(x, w_router, b_router, w_gate, w_up, w_down, top, activation, extra=None):
+def _plain_act(z, activation):
+    if activation == "relu_squared":
+        return torch.relu(z) ** 2
+    if activation == "relu":
+        return torch.relu(z)
+    if activation == "gelu_tanh":
+        return torch.nn.functional.gelu(z, approximate="tanh")
+    return torch.nn.functional.silu(z)
+
+
+def moe_feed_forward(x, w_router, b_router, w_gate, w_up, w_down, top, activation, extra=None,
+                     scores="chosen", correction=None, identity=0, extra_gated=False):
     T, d = x.shape
-    E = w_gate.shape[0]
-    z = x.float() @ w_router.float().t() + (b_router if b_router is not None else 0.0)
+    E = w_up.shape[0]
+    outputs = E + identity
+    z = x.float() @ w_router.float().t()
+    gate = torch.sigmoid(z[:, outputs]) if extra_gated else None
+    z = z[:, :outputs] + (b_router if b_router is not None else 0.0)
     out = torch.zeros((T, d), dtype=torch.float32)
     for t in range(T):
-        order = sorted(range(E), key=lambda e: (-float(z[t, e]), e))[:top]
-        w = torch.softmax(z[t, order], dim=0)
+        if scores == "all":
+            sc = torch.softmax(z[t], dim=0)
+            choice = sc + (correction if correction is not None else 0.0)
+            order = sorted(range(outputs), key=lambda e: (-float(choice[e]), e))[:top]
+            w = sc[order] / (sc[order].sum() + 1e-20)
+        else:
+            order = sorted(range(outputs), key=lambda e: (-float(z[t, e]), e))[:top]
+            w = torch.softmax(z[t, order], dim=0)
         for e, we in zip(order, w):
-            g = x[t].float() @ w_gate[e].float().t()
+            if e >= E:
+                out[t] += we * x[t].float()
+                continue
             u = x[t].float() @ w_up[e].float().t()
-            a = torch.nn.functional.silu(g) if activation == "silu" else \
-                torch.relu(g) if activation == "relu" else torch.nn.functional.gelu(g, approximate="tanh")
-            hid = (a * u).to(x.dtype).float()
-            out[t] += we * (hid @ w_down[e].float().t())
+            if w_gate is not None:
+                hid = _plain_act(x[t].float() @ w_gate[e].float().t(), activation) * u
+            else:
+                hid = _plain_act(u, activation)
+            out[t] += we * (hid.to(x.dtype).float() @ w_down[e].float().t())
     if extra is not None:
-        out += extra
+        out += extra * gate[:, None] if gate is not None else extra
     return out
+
+
+def act_rows(x, activation):
+    x.copy_(_plain_act(x.float(), activation).to(x.dtype))
+
+
+def stream_spread(h, x):
+    x.copy_(h.unsqueeze(0).expand_as(x))
+
+
+def _normed(u, gain, eps):
+    return u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * gain
+
+
+def stream_read_norm(x, cin, gain, eps, out):
+    out.copy_(_normed(torch.tensordot(cin, x, 1), gain, eps).to(out.dtype))
+
+
+def stream_write(x, y, mix, cout, eps=0.0, next_in=None, next_gain=None, next_out=None, sum_out=None):
+    S = x.shape[0]
+    new = torch.einsum("st,snd->tnd", mix.reshape(S, S), x) + cout[:, None, None] * y.float()[None]
+    x.copy_(new)
+    if next_out is not None:
+        next_out.copy_(_normed(torch.tensordot(next_in, x, 1), next_gain, eps).to(next_out.dtype))
+    if sum_out is not None:
+        sum_out.copy_(x.sum(0))
+
+
+def qkv_conv_rope_norm_cache(qkv, q_out, num_heads, num_kv_heads, key_dim, value_dim, conv_w, num_seqs,
+                             seq_ids, q_start, state_slots, state, conv_offset, rope, rotary_dim,
+                             interleaved, unit_norm, eps, slots, k_cache, v_cache, page_size):
+    T, C = qkv.shape
+    u = qkv.float()
+    y = u.clone()
+    taps = conv_w.shape[1] if conv_w is not None else 0
+    if taps:
+        keep = taps - 1
+        for b in range(num_seqs):
+            s, e = int(q_start[b]), int(q_start[b + 1])
+            kept = state[int(state_slots[b])][conv_offset:conv_offset + keep * C].view(keep, C) if keep \
+                else torch.zeros((0, C))
+            rows = torch.cat([kept.clone(), u[s:e]])
+            for t in range(s, e):
+                y[t] = (rows[t - s:t - s + taps] * conv_w.t()).sum(0)
+            if keep:
+                kept.copy_(rows[rows.shape[0] - keep:])
+    qw, kw = num_heads * key_dim, num_kv_heads * key_dim
+
+    def treat(z, heads):
+        z = _turn(z.reshape(T, heads, key_dim).clone(), rope, rotary_dim, interleaved)
+        if unit_norm:
+            z = z * torch.rsqrt((z * z).mean(-1, keepdim=True) + eps)
+        return z
+
+    q_out.copy_(treat(y[:, :qw], num_heads).reshape(T, -1).to(q_out.dtype))
+    kk = treat(y[:, qw:qw + kw], num_kv_heads)
+    vv = y[:, qw + kw:].reshape(T, num_kv_heads, value_dim)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = s // page_size, s % page_size
+        k_cache[page, :, off, :] = kk[t].to(k_cache.dtype)
+        v_cache[page, :, off, :] = vv[t].to(v_cache.dtype)
 
 
 def weighted_sum(parts, scales, out):
@@ -468,7 +561,8 @@ def _turn(y, rope, rot, interleaved):
 
 
 def qk_rownorm_rope_cache(q, k, v, num_heads, num_kv_heads, key_dim, value_dim, q_gain, k_gain, eps,
-                          rope, rotary_dim, interleaved, slots, k_cache, v_cache, page_size):
+                          rope, rotary_dim, interleaved, slots, k_cache, v_cache, page_size,
+                          positions=None, temp_coef=0.0, temp_every=0):
     T = q.shape[0]
 
     def treat(x, heads, gain):
@@ -477,7 +571,12 @@ def qk_rownorm_rope_cache(q, k, v, num_heads, num_kv_heads, key_dim, value_dim, 
             y = y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps) * gain
         return _turn(y.reshape(T, heads, key_dim).clone(), rope, rotary_dim, interleaved)
 
-    q.copy_(treat(q, num_heads, q_gain).reshape(T, -1).to(q.dtype))
+    qq = treat(q, num_heads, q_gain).reshape(T, -1)
+    if positions is not None and temp_every > 0:
+        steps = torch.div(positions.clamp(min=-1) + 1, temp_every, rounding_mode="floor") + 1
+        qq = qq * (1.0 + float(torch.tensor(temp_coef, dtype=torch.float32)) *
+                   torch.log(steps.float()))[:, None]
+    q.copy_(qq.to(q.dtype))
     if k is None:
         return
     kk = treat(k, num_kv_heads, k_gain)
@@ -591,7 +690,8 @@ def attention_sink_wide_supports(num_heads, num_kv_heads, key_dim, value_dim):
     return False
 
 
-NAMES = ["scaled_add_norm", "add_bias", "qk_rownorm_rope_cache", "latent_row_cache", "rope_slice",
+NAMES = ["act_rows", "stream_spread", "stream_read_norm", "stream_write", "qkv_conv_rope_norm_cache",
+         "scaled_add_norm", "add_bias", "qk_rownorm_rope_cache", "latent_row_cache", "rope_slice",
          "head_linear", "mlstm", "mlstm_chunked", "mlstm_chunk_tokens", "mlstm_chunked_supports",
          "gated_group_norm", "qkv_bias_rope_cache", "causal_conv_act", "selective_scan",
          "moe_feed_forward", "weighted_sum", "attention_sink_supports", "attention_sink_wide_supports", "rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",

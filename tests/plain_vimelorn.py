@@ -247,3 +247,13 @@ def forward_rounded(cfg, W, tokens):
         return forward(cfg, W, tokens)
     finally:
         globals()["rmsnorm"] = saved
+
+
+def greedy(cfg, W, prompt, n):
+    """n tokens after `prompt`, each the most likely next one (ties: the lower id)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(np.argmax(forward(cfg, W, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out

@@ -10,8 +10,9 @@ from plain_pack import plain_pack
 from tgo_b200.cache.pages import NULL_PAGE, GroupLayout, PagesExhausted, SlotsExhausted
 
 
-def make_manager(kind, pages=(12, 12), page=4, slots=3, window=10):
-    groups = [GroupLayout("full", None, 2, (2, 8), [0, 2]), GroupLayout("window", window, 2, (2, 8), [1])]
+def make_manager(kind, pages=(12, 12), page=4, slots=3, window=10, keep_first=0):
+    groups = [GroupLayout("full", None, 2, (2, 8), [0, 2]),
+              GroupLayout("window", window, 2, (2, 8), [1], keep_first=keep_first)]
     if kind == "native":
         from tgo_b200.cache.native import NativeCacheManager
         return NativeCacheManager(groups, page, list(pages), slots)
@@ -110,10 +111,12 @@ def test_freed_pages_are_used_again(manager):
     assert sorted(cm.requests["b"].held(0)) == first
 
 
+@pytest.mark.parametrize("keep", [0, 6, 9])
 @pytest.mark.parametrize("seed", range(5))
-def test_random_orders_keep_the_books(manager, seed):
+def test_random_orders_keep_the_books(manager, seed, keep):
+    """`keep`: the window group also holds the pages of every request's first tokens."""
     rng = random.Random(seed)
-    cm = manager(pages=(40, 40), page=4, slots=4, window=10)
+    cm = manager(pages=(40, 40), page=4, slots=4, window=10, keep_first=keep)
     live, counter = {}, 0
     for _ in range(600):
         action = rng.random()
@@ -146,6 +149,11 @@ def test_random_orders_keep_the_books(manager, seed):
                 cm.slot_of(r, 0, p)
             for p in range(max(0, n - 10 + 1), n):
                 cm.slot_of(r, 1, p)
+            for p in range(min(keep, n)):                       # and every kept first key
+                cm.slot_of(r, 1, p)
+            # nothing else: the kept pages, the window's, and no page between them
+            held = len(r.held(1))
+            assert held <= (keep + 3) // 4 + (10 + 3) // 4 + 1 or n <= keep + 10 + 4, (held, n)
     for rid in list(live):
         cm.finish(rid)
     assert all(p.free_count == p.num_pages for p in cm.pools)
@@ -154,16 +162,17 @@ def test_random_orders_keep_the_books(manager, seed):
         cm.finish("r1" if "r1" not in cm.requests else "nobody")
 
 
+@pytest.mark.parametrize("keep", [0, 6])
 @pytest.mark.parametrize("seed", range(4))
-def test_native_books_follow_the_plain_ones(seed):
+def test_native_books_follow_the_plain_ones(seed, keep):
     """The same random life of requests through both managers: the same slots, tables,
     refusals and released pages at every turn, and the same packed step."""
     import numpy as np
 
     from tgo_b200.engine.step import StepEntry
     rng = random.Random(100 + seed)
-    plain_cm = make_manager("plain", pages=(30, 30), page=4, slots=4, window=10)
-    native_cm = make_manager("native", pages=(30, 30), page=4, slots=4, window=10)
+    plain_cm = make_manager("plain", pages=(30, 30), page=4, slots=4, window=10, keep_first=keep)
+    native_cm = make_manager("native", pages=(30, 30), page=4, slots=4, window=10, keep_first=keep)
     live, counter = {}, 0
 
     def both(call, *args):

@@ -21,6 +21,11 @@
 // token's keys into `n_splits` ranges of key tiles, one CTA each: the partial results
 // (unnormalised O, maximum, sum) go to scratch and `attention_sink_join_kernel` joins them and
 // adds the sink.
+// `keep_first` > 0 (with a window): the first keep_first keys of a request stay visible to
+// every later query beside the window; the key tiles that hold them and lie before the
+// window's first tile are walked first, then the window's tiles (one list of tiles, which is
+// also what `n_splits` cuts). `dist_bias` (float32 [n_dist][H]): dist_bias[min(i - j, n_dist
+// - 1)][h] is added to the scaled score, unscaled (a learned bias by distance).
 #include "common.cuh"
 
 #define AS_BN 64                 // keys per tile
@@ -58,7 +63,8 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
                       int Hkv, int dk, int dv, float scale_log2, int window,
                       const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
-                      float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row) {
+                      float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row,
+                      int keep_first, const float* __restrict__ dist_bias, int n_dist) {
     constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
     constexpr int KS = DK / 16;
     constexpr int CHK = DK / 8, CHV = DV / 8;  // 16-byte chunks per padded row
@@ -88,12 +94,18 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
     // keys any row of the tile may read: [key_lo, key_hi)
     const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
     const int key_hi = p_last + 1;
-    int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    const int t_first = key_lo / AS_BN;        // the window's first tile
+    // tiles of kept first keys that lie before it; the walk is over v = 0 .. n_kept - 1 (those
+    // tiles), then the window's tiles: tile_of(v)
+    int n_kept = keep_first > 0 ? (keep_first + AS_BN - 1) / AS_BN : 0;
+    if (n_kept > t_first) n_kept = t_first;
+    int t_lo = 0, t_hi = n_kept + (key_hi + AS_BN - 1) / AS_BN - t_first;
     if (n_splits > 1) {                        // this CTA's share of the key tiles (it may be empty)
         const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
         t_lo += blockIdx.z * per;
         if (t_lo + per < t_hi) t_hi = t_lo + per;
     }
+    auto tile_of = [&](int v) { return v < n_kept ? v : t_first + (v - n_kept); };
     const int chk = dk / 8, chv = dv / 8;      // chunks a real row has
 
     for (int i = tid; i < AS_BM * CHK; i += THREADS) {
@@ -108,7 +120,7 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
         for (int i = tid; i < AS_BN * CHK; i += THREADS) {
             const int r = i / CHK, c = i % CHK;
             const int j = t * AS_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            const bool ok = (j >= key_lo || j < keep_first) && j < key_hi && c < chk;
             size_t off = 0;
             if (ok) {
                 const int pi = j / page_size, po = j - pi * page_size;
@@ -119,7 +131,7 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
         for (int i = tid; i < AS_BN * CHV; i += THREADS) {
             const int r = i / CHV, c = i % CHV;
             const int j = t * AS_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chv;
+            const bool ok = (j >= key_lo || j < keep_first) && j < key_hi && c < chv;
             size_t off = 0;
             if (ok) {
                 const int pi = j / page_size, po = j - pi * page_size;
@@ -128,12 +140,13 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
             cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
         }
     };
-    if (t_lo < t_hi) load_kv(t_lo, 0);
+    if (t_lo < t_hi) load_kv(tile_of(t_lo), 0);
     cp_async_commit();
 
     float o[AS_RW][DV / 8][4];
     float m_run[AS_RW][2], l_run[AS_RW][2];
     int pos_row[AS_RW][2], vis_row[AS_RW][2];
+    const float* bias_row[AS_RW][2];           // the distance bias's column of each row's head
 #pragma unroll
     for (int rw = 0; rw < AS_RW; ++rw) {
 #pragma unroll
@@ -145,13 +158,19 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
             l_run[rw][h] = 0.f;
             pos_row[rw][h] = r < n_rows ? p0 + r / G : -1;      // rows beyond the tile read nothing
             vis_row[rw][h] = (window > 0 && pos_row[rw][h] - window + 1 > 0) ? pos_row[rw][h] - window + 1 : 0;
+            bias_row[rw][h] = dist_bias ? dist_bias + kvh * G + (r < n_rows ? r % G : 0) : nullptr;
         }
     }
     const bool warp_active = warp * AS_RW * 16 < n_rows;
+    // a scaled (and capped) score with the bias of its distance, as an exponent in base 2
+    auto biased = [&](float sc, const float* col, int dist) {
+        return col ? fmaf(col[(size_t)(dist < n_dist ? dist : n_dist - 1) * H], AS_LOG2E, sc) : sc;
+    };
 
-    for (int t = t_lo; t < t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+    for (int vt_i = t_lo; vt_i < t_hi; ++vt_i) {
+        const int t = tile_of(vt_i);
+        const int buf = (vt_i - t_lo) & 1;
+        if (vt_i + 1 < t_hi) load_kv(tile_of(vt_i + 1), buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -197,10 +216,12 @@ attention_sink_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __re
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = kbase + i * 8 + e;
-                        const bool a = full || (j <= pos_row[rw][0] && j >= vis_row[rw][0]);
-                        const bool c = full || (j <= pos_row[rw][1] && j >= vis_row[rw][1]);
-                        s[rw][i][e] = a ? as_scored(s[rw][i][e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
-                        s[rw][i][2 + e] = c ? as_scored(s[rw][i][2 + e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                        const bool a = full || (j <= pos_row[rw][0] && (j >= vis_row[rw][0] || j < keep_first));
+                        const bool c = full || (j <= pos_row[rw][1] && (j >= vis_row[rw][1] || j < keep_first));
+                        s[rw][i][e] = a ? biased(as_scored(s[rw][i][e], scale_log2, cap_log2, scale_over_cap),
+                                                 bias_row[rw][0], pos_row[rw][0] - j) : -INFINITY;
+                        s[rw][i][2 + e] = c ? biased(as_scored(s[rw][i][2 + e], scale_log2, cap_log2, scale_over_cap),
+                                                     bias_row[rw][1], pos_row[rw][1] - j) : -INFINITY;
                         mx[0] = fmaxf(mx[0], s[rw][i][e]);
                         mx[1] = fmaxf(mx[1], s[rw][i][2 + e]);
                     }
@@ -314,7 +335,8 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                              const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
                              int Hkv, int dk, int dv, float scale_log2, int window,
                              const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
-                             float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row) {
+                             float* __restrict__ part_ml, float cap_log2, float scale_over_cap, int v_row,
+                             int keep_first, const float* __restrict__ dist_bias, int n_dist) {
     constexpr int LDK = DK + AS_PAD, LDV = DV + AS_PAD;
     constexpr int KS = DK / 16;
     constexpr int CHK = DK / 8, CHV = DV / 8;
@@ -337,26 +359,32 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const int* bt = block_tables + (size_t)seq_ids[tok] * max_blocks;
     const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int key_hi = p + 1;
-    int t_lo = key_lo / AS_BN, t_hi = (key_hi + AS_BN - 1) / AS_BN;
+    const int t_first = key_lo / AS_BN;        // the window's first tile
+    // tiles of kept first keys before it are walked first: v = 0 .. n_kept - 1, then the window's
+    int n_kept = keep_first > 0 ? (keep_first + AS_BN - 1) / AS_BN : 0;
+    if (n_kept > t_first) n_kept = t_first;
+    int t_lo = 0, t_hi = n_kept + (key_hi + AS_BN - 1) / AS_BN - t_first;
     if (n_splits > 1) {
         const int per = (t_hi - t_lo + n_splits - 1) / n_splits;
         t_lo += split * per;
         if (t_lo + per < t_hi) t_hi = t_lo + per;
     }
+    auto tile_of = [&](int v) { return v < n_kept ? v : t_first + (v - n_kept); };
     const int chk = dk / 8, chv = dv / 8;
-    // this CTA's slice of the block table -> shared memory, so that the address of a row is
-    // not a chain of two global loads
+    // this CTA's slice of the block table (the window's part of its share) -> shared memory, so
+    // that the address of a row is not a chain of two global loads
     __shared__ int s_pages[AS_PAGES];
-    const int pg_lo = (t_lo * AS_BN) / page_size;
+    const int w_lo = t_lo > n_kept ? t_lo : n_kept;       // first walk index inside the window
+    const int pg_lo = w_lo < t_hi ? (tile_of(w_lo) * AS_BN) / page_size : 0;
     {
-        int pg_hi = (t_hi * AS_BN + page_size - 1) / page_size;
+        int pg_hi = w_lo < t_hi ? (tile_of(t_hi - 1) * AS_BN + AS_BN + page_size - 1) / page_size : 0;
         if (pg_hi > max_blocks) pg_hi = max_blocks;
         if (pg_hi - pg_lo > AS_PAGES) pg_hi = pg_lo + AS_PAGES;
         for (int i = pg_lo + tid; i < pg_hi; i += 128) s_pages[i - pg_lo] = bt[i];
     }
     __syncthreads();
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
-    auto page_of = [&](int pi) { return pi - pg_lo < AS_PAGES ? s_pages[pi - pg_lo] : bt[pi]; };
+    auto page_of = [&](int pi) { return (pi >= pg_lo && pi - pg_lo < AS_PAGES) ? s_pages[pi - pg_lo] : bt[pi]; };
     for (int i = tid; i < 16 * CHK; i += 128) {
         const int r = i / CHK, c = i % CHK;
         const bool ok = r < G && c < chk;
@@ -369,7 +397,7 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         for (int i = tid; i < AS_BN * CHK; i += 128) {
             const int r = i / CHK, c = i % CHK;
             const int j = t * AS_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chk;
+            const bool ok = (j >= key_lo || j < keep_first) && j < key_hi && c < chk;
             size_t off = 0;
             if (ok) {
                 const int pi = page_shift >= 0 ? j >> page_shift : j / page_size, po = j - pi * page_size;
@@ -380,7 +408,7 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         for (int i = tid; i < AS_BN * CHV; i += 128) {
             const int r = i / CHV, c = i % CHV;
             const int j = t * AS_BN + r;
-            const bool ok = j >= key_lo && j < key_hi && c < chv;
+            const bool ok = (j >= key_lo || j < keep_first) && j < key_hi && c < chv;
             size_t off = 0;
             if (ok) {
                 const int pi = page_shift >= 0 ? j >> page_shift : j / page_size, po = j - pi * page_size;
@@ -389,7 +417,7 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             cp_async16(dvs + r * LDV + c * 8, v_cache + off, ok);
         }
     };
-    if (t_lo < t_hi) load_kv(t_lo, 0);
+    if (t_lo < t_hi) load_kv(tile_of(t_lo), 0);
     cp_async_commit();
 
     float o[DV / 8][4];
@@ -399,14 +427,20 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const bool row_lo_ok = r_lo < G, row_hi_ok = r_hi < G;
     uint32_t qa[KS][4];
+    const float* bias_lo = dist_bias ? dist_bias + kvh * G + (row_lo_ok ? r_lo : 0) : nullptr;
+    const float* bias_hi = dist_bias ? dist_bias + kvh * G + (row_hi_ok ? r_hi : 0) : nullptr;
+    auto biased = [&](float sc, const float* col, int dist) {
+        return col ? fmaf(col[(size_t)(dist < n_dist ? dist : n_dist - 1) * H], AS_LOG2E, sc) : sc;
+    };
 
-    for (int t = t_lo; t < t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+    for (int vt_i = t_lo; vt_i < t_hi; ++vt_i) {
+        const int t = tile_of(vt_i);
+        const int buf = (vt_i - t_lo) & 1;
+        if (vt_i + 1 < t_hi) load_kv(tile_of(vt_i + 1), buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (t == t_lo) {
+        if (vt_i == t_lo) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks)
                 ldmatrix_x4(qa[ks], sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
@@ -430,9 +464,11 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = kbase + i * 8 + e;
-                const bool vis = j >= key_lo && j < key_hi;
-                s[i][e] = (vis && row_lo_ok) ? as_scored(s[i][e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
-                s[i][2 + e] = (vis && row_hi_ok) ? as_scored(s[i][2 + e], scale_log2, cap_log2, scale_over_cap) : -INFINITY;
+                const bool vis = (j >= key_lo || j < keep_first) && j < key_hi;
+                s[i][e] = (vis && row_lo_ok) ? biased(as_scored(s[i][e], scale_log2, cap_log2, scale_over_cap),
+                                                      bias_lo, p - j) : -INFINITY;
+                s[i][2 + e] = (vis && row_hi_ok) ? biased(as_scored(s[i][2 + e], scale_log2, cap_log2, scale_over_cap),
+                                                          bias_hi, p - j) : -INFINITY;
                 mx_lo = fmaxf(mx_lo, s[i][e]);
                 mx_hi = fmaxf(mx_hi, s[i][2 + e]);
             }
@@ -1031,7 +1067,8 @@ static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long o
                        int max_blocks, const int* positions, const int* seq_ids, const int* tile_tok0,
                        const int* tile_ntok, int n_tiles, int H, int Hkv, int dk, int dv, float scale,
                        int window, const float* sinks, int n_splits, float* part_o, float* part_ml,
-                       float softcap, int v_row, cudaStream_t stream) {
+                       float softcap, int v_row, int keep_first, const float* dist_bias, int n_dist,
+                       cudaStream_t stream) {
     const float cap_log2 = softcap > 0.f ? softcap * AS_LOG2E : 0.f;
     const float scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
     const size_t smem = ((size_t)AS_BM * (DK + AS_PAD) + 2 * AS_BN * (DK + AS_PAD) + 2 * AS_BN * (DV + AS_PAD)) *
@@ -1048,14 +1085,14 @@ static int launch_sink(const bf16* q, long long q_stride, bf16* out, long long o
         rc = tgo_launch_pdl(dec, dim3(n_tiles, Hkv, n_splits), dim3(128), dsm, stream, q, q_stride, out,
                             out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions, seq_ids,
                             H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o, part_ml,
-                            cap_log2, scale_over_cap, v_row);
+                            cap_log2, scale_over_cap, v_row, keep_first, dist_bias, n_dist);
     } else {
         auto kernel = attention_sink_kernel<DK, DV>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kernel<<<dim3(n_tiles, Hkv, n_splits), AS_WARPS * 32, smem, stream>>>(
             q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks, positions,
             seq_ids, tile_tok0, tile_ntok, H, Hkv, dk, dv, scale * AS_LOG2E, window, sinks, n_splits, part_o,
-            part_ml, cap_log2, scale_over_cap, v_row);
+            part_ml, cap_log2, scale_over_cap, v_row, keep_first, dist_bias, n_dist);
         rc = launch_status();
     }
     if (rc || n_splits <= 1) return rc;
@@ -1075,10 +1112,13 @@ TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, lon
                                const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                int n_tiles, int H, int Hkv, int dk, int dv, float scale, int window,
                                const float* sinks, int n_splits, float* part_o, float* part_ml,
-                               float softcap, int v_row, cudaStream_t stream) {
+                               float softcap, int v_row, int keep_first, const float* dist_bias,
+                               int n_dist, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (v_row <= 0) v_row = dv;
-    if (v_row < dv || (v_row % 8) || !(softcap >= 0.f)) return TGO_E_BAD_ARG;
+    if (v_row < dv || (v_row % 8) || !(softcap >= 0.f) || keep_first < 0 || (dist_bias && n_dist <= 0))
+        return TGO_E_BAD_ARG;
+    if (window == 0) keep_first = 0;
     if (!tgo_attention_sink_supports(H, Hkv, dk, dv) || page_size <= 0 || max_blocks <= 0 || window < 0 ||
         Hkv > 65535 || (q_stride % 8) || (out_stride % 2) || ((uintptr_t)q % 16) || ((uintptr_t)out % 4) ||
         ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16) || (!tile_tok0) != (!tile_ntok) ||
@@ -1089,7 +1129,8 @@ TGO_API int tgo_attention_sink(const void* q, long long q_stride, void* out, lon
                                           (const bf16*)k_cache, (const bf16*)v_cache, page_size,          \
                                           block_tables, max_blocks, positions, seq_ids, tile_tok0,        \
                                           tile_ntok, n_tiles, H, Hkv, dk, dv, scale, window, sinks,   \
-                                          n_splits, part_o, part_ml, softcap, v_row, stream)
+                                          n_splits, part_o, part_ml, softcap, v_row, keep_first, dist_bias, \
+                                          n_dist, stream)
     if (dk <= 64) return dv <= 64 ? AS_GO(64, 64) : AS_GO(64, 128);
     return dv <= 64 ? AS_GO(128, 64) : AS_GO(128, 128);
 #undef AS_GO

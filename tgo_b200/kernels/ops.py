@@ -382,19 +382,23 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
                         positions: torch.Tensor, scale: float, window: int,
                         sinks: Optional[torch.Tensor], tile_tok0: Optional[torch.Tensor] = None,
                         tile_ntok: Optional[torch.Tensor] = None, n_splits: int = 1,
-                        softcap: float = 0.0, value_row: int = 0) -> None:
-    """`softcap` and `value_row` as in `attention_generic`.
+                        softcap: float = 0.0, value_row: int = 0, keep_first: int = 0,
+                        dist_bias: Optional[torch.Tensor] = None) -> None:
+    """`softcap`, `value_row`, `keep_first` and `dist_bias` as in `attention_generic`.
     Paged causal attention with keys `key_dim` and values `value_dim` wide, a window (0:
     none) and a sink per head (float32 [H] or None), bfloat16 on the tensor cores: a block per
     tile of consecutive tokens of one request (tile_tok0, tile_ntok: int32; None: every token
     is a tile of its own) and kv head. Without tile lists, `n_splits` > 1 cuts every token's
     keys over as many blocks and a second kernel joins their shares."""
-    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks, tile_tok0, tile_ntok)
+    _need_cuda(q, out, k_cache, v_cache, block_tables, seq_ids, positions, sinks, tile_tok0, tile_ntok,
+               dist_bias)
     assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_tables.is_contiguous()
     assert block_tables.dtype == torch.int32 and block_tables.dim() == 2
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and
+                                 dist_bias.shape[1] == num_heads and dist_bias.is_contiguous())
     if tile_tok0 is not None:
         assert tile_tok0.dtype == torch.int32 and tile_ntok.dtype == torch.int32
         n_tiles = tile_tok0.numel()
@@ -413,7 +417,8 @@ def attention_sink_tile(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
         c_int(num_kv_heads), c_int(key_dim), c_int(value_dim), c_float(scale), c_int(window),
         _ptr(sinks), c_int(n_splits), _ptr(part_o), _ptr(part_ml), c_float(softcap or 0.0),
-        c_int(value_row), _stream()), "attention_sink",
+        c_int(value_row), c_int(keep_first), _ptr(dist_bias),
+        c_int(dist_bias.shape[0] if dist_bias is not None else 0), _stream()), "attention_sink",
         f"(heads={num_heads}/{num_kv_heads}, dk={key_dim}, dv={value_dim})")
     if n_splits > 1:
         LAUNCHES[0] += 1

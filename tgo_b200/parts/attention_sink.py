@@ -248,8 +248,8 @@ def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, sof
     and other sizes: the generic kernel (a warp per token and head, keys in a fixed order)."""
     v_cache = cache.k if value_row else cache.v
     form, tokens = tile_form(H, Hkv, dk, dv, value_row, q.dtype)
-    if keep_first or dist_bias is not None:
-        form = None                     # the tile kernels know neither
+    if form == "wide" and (keep_first or dist_bias is not None):
+        form = None                     # the kernel for wide rows knows neither
     if form is not None and ops.attention_sink_takes(q, out):
         tok0, ntok = (None, None) if ctx.decode_only else step_tiles(ctx, tokens)
         if form == "wide":
@@ -264,7 +264,8 @@ def sink_attention(q, out, H, Hkv, dk, dv, cache, ctx, scale, window, sinks, sof
         splits = decode_splits(ctx, Hkv, window, q.device) if ctx.decode_only else 1
         ops.attention_sink_tile(q, out, H, Hkv, dk, dv, cache.k, v_cache, cache.page_size,
                                 cache.block_tables, ctx.seq_ids, ctx.positions, scale, window, sinks,
-                                tok0, ntok, n_splits=splits, softcap=softcap, value_row=value_row)
+                                tok0, ntok, n_splits=splits, softcap=softcap, value_row=value_row,
+                                keep_first=keep_first, dist_bias=dist_bias)
         return
     ops.attention_generic(q, out, H, Hkv, dk, cache.k, v_cache, cache.page_size,
                           cache.block_tables, ctx.seq_ids, ctx.positions, scale, window,
