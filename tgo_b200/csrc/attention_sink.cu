@@ -376,15 +376,13 @@ attention_sink_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     __shared__ int s_pages[AS_PAGES];
     const int w_lo = t_lo > n_kept ? t_lo : n_kept;       // first walk index inside the window
     const int pg_lo = w_lo < t_hi ? (tile_of(w_lo) * AS_BN) / page_size : 0;
-    {
-        int pg_hi = w_lo < t_hi ? (tile_of(t_hi - 1) * AS_BN + AS_BN + page_size - 1) / page_size : 0;
-        if (pg_hi > max_blocks) pg_hi = max_blocks;
-        if (pg_hi - pg_lo > AS_PAGES) pg_hi = pg_lo + AS_PAGES;
-        for (int i = pg_lo + tid; i < pg_hi; i += 128) s_pages[i - pg_lo] = bt[i];
-    }
+    int pg_hi = w_lo < t_hi ? (tile_of(t_hi - 1) * AS_BN + AS_BN + page_size - 1) / page_size : 0;
+    if (pg_hi > max_blocks) pg_hi = max_blocks;
+    if (pg_hi - pg_lo > AS_PAGES) pg_hi = pg_lo + AS_PAGES;
+    for (int i = pg_lo + tid; i < pg_hi; i += 128) s_pages[i - pg_lo] = bt[i];
     __syncthreads();
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
-    auto page_of = [&](int pi) { return (pi >= pg_lo && pi - pg_lo < AS_PAGES) ? s_pages[pi - pg_lo] : bt[pi]; };
+    auto page_of = [&](int pi) { return (pi >= pg_lo && pi < pg_hi) ? s_pages[pi - pg_lo] : bt[pi]; };
     for (int i = tid; i < 16 * CHK; i += 128) {
         const int r = i / CHK, c = i % CHK;
         const bool ok = r < G && c < chk;
