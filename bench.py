@@ -451,6 +451,62 @@ def derosun_beside_gafonex(args):
     return 0
 
 
+def vimelorn_config(width, heads, kv, dim, ff, layers, vocab=32768):
+    """(windowed, windowed with routed experts, causal) repeated, four residual streams: windowed
+    attention of the given heads over 1024 keys and the first 4, a convolution of 4 taps on q, k
+    and v and a whole-head rotation; routed feed-forwards of 32 small experts and 2 identity
+    ones, top 4, with a gated shared expert (as much active width as Totatar's); causal
+    attention with whole-row q/k norms, a query temperature and a bias by distance."""
+    win = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "conv": 4, "scale": dim ** -0.5,
+           "rot": {"dims": dim, "base": 5e5}, "mask": {"size": 1024, "keep_first": 4}}
+    cau = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "bias_max": 4096, "q_temp": {"coef": 0.1, "every": 256}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 32, "identity": 2, "top": 4}, "expert": {"ff": ff // 8},
+           "shared": {"ff": ff // 2}}
+    order = ({"type": "attention", "mixer": win, "mlp": dense}, {"type": "attention", "mixer": win, "mlp": moe},
+             {"type": "attention_2", "mixer": cau, "mlp": dense})
+    return {"architecture": "Vimelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "streams": 4, "embedding": {"scale": 1.0}, "layers": [order[i % 3] for i in range(layers)]}
+
+
+def vimelorn_beside_totatar(args):
+    """One JSON line per measurement: prefill of 2,048 tokens and decode at batch 8 and 64 for
+    Vimelorn, for Totatar (the closest model the engine has by its mechanisms: a windowed
+    attention, short convolutions, routed experts with a shared one) and for Qwen3 (the closest
+    by its shape: attention in every layer), at each size; then Vimelorn's kernels one by one
+    beside their like kernels."""
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
+    from tgo_b200.engine.measure_kernels import measure_vimelorn_kernels
+    peaks = load_peaks()
+    layers = args.layers or 6
+    steps = min(args.steps, 64)
+    for name, (width, heads, kv, dim, ff) in DESIGN_SIZES.items():
+        for arch, make in (("vimelorn", vimelorn_config), ("totatar", totatar_config), ("qwen3", qwen3_config)):
+            model = tgo_b200.open_random(make(width, heads, kv, dim, ff, layers), seed=SEED,
+                                         dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+            pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=3, seed=SEED, page_size=PAGE)
+            rec = {"size": name, "model": arch, "layers": layers,
+                   "prefill_ms": round(pre["ms"], 3), "prefill_tokens_per_s": round(pre["tokens_per_s"]),
+                   "prefill_frac_of_library_peak": round(pre["tflops"] / peaks["bf16_tflops"], 3)}
+            for b in (8, 64):
+                r = measure_decode(model, b, PROMPT, steps, warmup=max(args.warmup, 3), seed=SEED,
+                                   page_size=PAGE)
+                rec[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+                rec[f"decode_b{b}_tokens_per_s"] = round(r["tokens_per_s"])
+                rec[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            print(json.dumps(rec), flush=True)
+            del model
+            torch.cuda.empty_cache()
+        for rec in measure_vimelorn_kernels(width, heads, kv, dim, dim, 1024, 4, 4, 4, 32, 2, 4, ff // 8):
+            rec["size"] = name
+            print(json.dumps(rec), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -465,7 +521,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
     ap.add_argument("--rows", default="256,512,1024,2048", help="with --only products: row counts")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products",
-                                                   "gafonex", "totatar", "derosun"],
+                                                   "gafonex", "totatar", "derosun", "vimelorn"],
                     help="run just the 2,048-token prefill, just the decode steps, the "
                          "continuous-batching workload, or the exactness check at real layer "
                          "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
@@ -477,7 +533,10 @@ def main():
                          "Totatar design (state-space, parallel attention and routed layers) "
                          "beside Gafonex in the same way; derosun: the Derosun design (matrix "
                          "memory, capped attention and latent attention layers) beside Gafonex "
-                         "in the same way")
+                         "in the same way; vimelorn: the Vimelorn design (several residual "
+                         "streams, windowed attention that keeps the first keys, attention with "
+                         "a bias by distance, routed small experts) beside Totatar and Qwen3 in "
+                         "the same way")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -500,6 +559,8 @@ def main():
         return totatar_beside_gafonex(args)
     if args.only == "derosun":
         return derosun_beside_gafonex(args)
+    if args.only == "vimelorn":
+        return vimelorn_beside_totatar(args)
     config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers

@@ -583,15 +583,155 @@ def measure_derosun_kernels(width: int, heads: int, kv_heads: int, key_dim: int,
     return out
 
 
+def measure_vimelorn_kernels(width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                             window: int, keep_first: int, taps: int, streams: int, experts: int,
+                             identity: int, top: int, expert_ff: int, prompt: int = 2048, batch: int = 64,
+                             context: int = 2048, page: int = 16, device="cuda:0") -> List[Dict[str, object]]:
+    """The kernels of the layers that keep several residual streams, convolve their projection
+    rows, keep the first keys beside a window, add a bias by distance and route to small experts
+    among which some are the identity, each timed alone beside the like kernel of the framework's
+    closest layers at equal sizes (same timing and denominators as `measure_kernels`)."""
+    from types import SimpleNamespace
+
+    from ..parts.attention_sink import bias_by_distance, sink_attention
+    dev = torch.device(device)
+    peaks = load_peaks()
+    hbm, tc, fma = peaks["hbm_gbs"], peaks["bf16_tflops"], _fma_tflops(dev)
+    flush = L2Flusher(dev)
+    out: List[Dict[str, object]] = []
+    bf = torch.bfloat16
+
+    def row(name, ms, like, like_ms, bound, work, like_work=None):
+        peak = {"hbm": hbm * 1e9, "tensor": tc * 1e12, "fma": fma * 1e12}[bound]
+        rec = {"kernel": name, "us": round(ms * 1e3, 1), "bound": bound,
+               "frac": round(work / (ms * 1e-3) / peak, 4)}
+        if like:
+            rec.update(like=like, like_us=round(like_ms * 1e3, 1),
+                       like_frac=round((like_work or work) / (like_ms * 1e-3) / peak, 4))
+        out.append(rec)
+
+    def context_of(n_req, extent, first):
+        T = n_req * extent
+        pos = (torch.arange(extent, dtype=torch.int32, device=dev) + first).repeat(n_req)
+        seq = torch.arange(n_req, dtype=torch.int32, device=dev).repeat_interleave(extent)
+        qs = torch.arange(n_req + 1, dtype=torch.int32, device=dev) * extent
+        z = torch.zeros(n_req, dtype=torch.int32, device=dev)
+        return StepContext(T, n_req, pos, pos, seq, qs, z, torch.arange(n_req, dtype=torch.int32, device=dev),
+                           z, bf, extents=[extent] * n_req, first_positions=[first] * n_req,
+                           max_extent=extent, max_context=first + extent, decode_only=extent == 1)
+
+    H, G, dk, dv = heads, kv_heads, key_dim, value_dim
+    scale = 1.0 / math.sqrt(dk)
+    table_rel = bias_by_distance(torch.randn((32, H), device=dev), 4 * window)
+    cases = ((1, prompt, 0, f"{prompt} tokens"), (batch, 1, context - 1, f"batch {batch} x {context} keys"))
+    # ---- attention: the window with kept first keys beside the window alone; the bias by
+    # distance beside plain causal attention (the same tile kernels without the extra)
+    for n_req, extent, first, what in cases:
+        kc, table = _paged(n_req, first + extent, G, dk, page, dev)
+        vc, _ = _paged(n_req, first + extent, G, dv, page, dev)
+        ctx = context_of(n_req, extent, first)
+        T = n_req * extent
+        q = torch.randn((T, H * dk), device=dev).to(bf)
+        o = torch.empty((T, H * dv), dtype=bf, device=dev)
+        cache = SimpleNamespace(k=kc, v=vc, page_size=page, block_tables=table)
+        ms = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, window, None,
+                                           keep_first=keep_first), flush)
+        like_ms = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, window, None), flush)
+        ms_b = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, 0, None,
+                                             dist_bias=table_rel), flush)
+        like_b = _timed(lambda: sink_attention(q, o, H, G, dk, dv, cache, ctx, scale, 0, None), flush)
+        if extent > 1:
+            keys = sum(min(t + 1, window) + min(keep_first, max(0, t + 1 - window)) for t in range(prompt))
+            row(f"attention, window {window} + first {keep_first}, {what}", ms, "the window alone", like_ms,
+                "tensor", 2.0 * H * (dk + dv) * keys, 2.0 * H * (dk + dv) * sum(min(t + 1, window) for t in range(prompt)))
+            row(f"attention with a bias by distance, {what}", ms_b, "plain causal", like_b, "tensor",
+                2.0 * H * (dk + dv) * (prompt * (prompt + 1) / 2))
+        else:
+            reach = min(window, context)
+            row(f"attention, window {window} + first {keep_first}, {what}", ms, "the window alone", like_ms,
+                "hbm", 2.0 * n_req * (reach + keep_first) * G * (dk + dv), 2.0 * n_req * reach * G * (dk + dv))
+            row(f"attention with a bias by distance, {what}", ms_b, "plain causal", like_b, "hbm",
+                2.0 * n_req * context * G * (dk + dv))
+    # ---- projection rows: convolution, rotation, unit norm, cache write, beside the biased rows
+    C = H * dk + G * (dk + dv)
+    conv = torch.randn((C, taps), device=dev)
+    for n_req, extent, first, what in ((1, prompt, 0, f"{prompt} rows"), (batch, 1, context - 1, f"batch {batch}")):
+        T = n_req * extent
+        ctx = context_of(n_req, extent, first)
+        qkv = torch.randn((T, C), device=dev).to(bf)
+        qq, kk, vv = qkv[:, :H * dk], qkv[:, H * dk:(H + G) * dk], qkv[:, (H + G) * dk:]
+        q_out = torch.empty((T, H * dk), dtype=bf, device=dev)
+        kc, _ = _paged(1, T, G, dk, page, dev)
+        vc, _ = _paged(1, T, G, dv, page, dev)
+        slots = torch.arange(T, dtype=torch.int32, device=dev) + page
+        rope = torch.randn((T, dk), device=dev)
+        state = torch.zeros((n_req + 1, (taps - 1) * C), device=dev)
+        ms = _timed(lambda: ops.qkv_conv_rope_norm_cache(qkv, q_out, H, G, dk, dv, conv, n_req, ctx.seq_ids,
+                                                         ctx.q_start, ctx.state_slots, state, 0, rope, dk, False,
+                                                         True, 1e-6, slots, kc, vc, page), flush)
+        bq, bk, bv = (torch.randn(n, device=dev) for n in (H * dk, G * dk, G * dv))
+        like_ms = _timed(lambda: ops.qkv_bias_rope_cache(qq, kk, vv, H, G, dk, dv, bq, bk, bv, rope, dk, False,
+                                                         slots, kc, vc, page), flush)
+        row(f"qkv_conv_rope_norm_cache + kept rows, {what}", ms, "qkv_bias_rope_cache", like_ms, "hbm",
+            2.0 * T * (2 * H * dk + 2 * G * (dk + dv)) + 8.0 * n_req * (taps - 1) * C,
+            2.0 * T * (2 * H * dk + 2 * G * (dk + dv)))
+    # ---- the streams: read with the norm, write with the next read, beside add + norm
+    S = streams
+    for T, what in ((prompt, f"{prompt} rows"), (batch, f"batch {batch}")):
+        x = torch.randn((S, T, width), device=dev)
+        y = torch.randn((T, width), device=dev)
+        h = torch.randn((T, width), device=dev)
+        cin, cout, mix = torch.randn(S, device=dev), torch.randn(S, device=dev), torch.randn((S, S), device=dev)
+        gain = torch.ones(width, device=dev)
+        n = torch.empty((T, width), dtype=bf, device=dev)
+        ms = _timed(lambda: ops.stream_read_norm(x, cin, gain, 1e-6, n), flush)
+        like_ms = _timed(lambda: ops.add_rmsnorm(h, None, gain, 1e-6, n), flush)
+        row(f"stream_read_norm ({S} streams), {what}", ms, "add_rmsnorm", like_ms, "hbm",
+            T * width * (4.0 * S + 2), T * width * (4.0 + 2))
+        ms = _timed(lambda: ops.stream_write(x, y, mix, cout, 1e-6, cin, gain, n), flush)
+        like_ms = _timed(lambda: ops.add_rmsnorm(h, y, gain, 1e-6, n), flush)
+        row(f"stream_write with the next read ({S} streams), {what}", ms, "add_rmsnorm with the add", like_ms,
+            "hbm", T * width * (8.0 * S + 4 + 2), T * width * (4.0 + 4 + 4 + 2))
+    # ---- routed experts: small ones without a gate, identity experts, scores over all, beside
+    # the gated routed experts of equal active width
+    E, ff = experts, expert_ff
+    wr = torch.randn((E + identity + 1, width), device=dev) * 0.05
+    corr = torch.randn(E + identity, device=dev) * 0.01
+    wu = (torch.randn((E, ff, width), device=dev) * 0.02).to(bf)
+    wd = (torch.randn((E, width, ff), device=dev) * 0.02).to(bf)
+    ffg = 2 * ff // 3 // 8 * 8                           # a gated expert of about equal work
+    wr2 = torch.randn((E, width), device=dev) * 0.05
+    wg2, wu2 = ((torch.randn((E, ffg, width), device=dev) * 0.02).to(bf) for _ in range(2))
+    wd2 = (torch.randn((E, width, ffg), device=dev) * 0.02).to(bf)
+    for T, what in ((prompt, f"{prompt} tokens"), (batch, f"batch {batch}"), (8, "batch 8")):
+        x = torch.randn((T, width), device=dev).to(bf)
+        extra = torch.randn((T, width), device=dev)
+        ms = _timed(lambda: ops.moe_feed_forward(x, wr, None, None, wu, wd, top, "relu_squared", extra, "all",
+                                                 corr, identity, True), flush)
+        like_ms = _timed(lambda: ops.moe_feed_forward(x, wr2, None, wg2, wu2, wd2, top, "silu", extra), flush)
+        like = f"gated routed experts (ff {ffg}, scores over the chosen)"
+        share = E / (E + identity)                       # of the chosen, about this many have matrices
+        if T >= 1024:
+            row(f"routed experts ({E} + {identity} identity, top {top}, ff {ff}, no gate), {what}", ms, like,
+                like_ms, "tensor", 2.0 * T * top * share * 2 * width * ff, 2.0 * T * top * 3 * width * ffg)
+        else:
+            touched = min(E, T * top)
+            row(f"routed experts ({E} + {identity} identity, top {top}, ff {ff}, no gate), {what}", ms, like,
+                like_ms, "hbm", 2.0 * touched * 2 * width * ff, 2.0 * touched * 3 * width * ffg)
+    return out
+
+
 if __name__ == "__main__":
-    # python -m tgo_b200.engine.measure_kernels derosun|totatar|gafonex [width]: the kernels of one design
+    # python -m tgo_b200.engine.measure_kernels vimelorn|derosun|totatar|gafonex [width]: the kernels of one design
     # at one size, a JSON line each (small enough to run under a profiler)
     import json
     import sys
     design = sys.argv[1] if len(sys.argv) > 1 else "totatar"
     w = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
     ff = 3 * w
-    if design == "derosun":
+    if design == "vimelorn":
+        recs = measure_vimelorn_kernels(w, 16, 4, 128, 128, 1024, 4, 4, 4, 32, 2, 4, ff // 8)
+    elif design == "derosun":
         recs = measure_derosun_kernels(w, 16, 4, 128, 128, 30.0, 512, 64, 3 * w // 4, w // 256, 128, 256, ff)
     elif design == "totatar":
         recs = measure_totatar_kernels(w, 16, 4, 128, 128, 1024, 2 * w // 64, 64, 128, 8, 4, 32, 4, ff // 8, ff)

@@ -75,10 +75,12 @@ def seeded_normal(n: int, seed: int, device="cpu") -> torch.Tensor:
 
 def random_tensor(spec: WeightSpec, seed: int, sigma: float, gain_sigma: float,
                   dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    # an extent that only a checkpoint's own tensor gives (declared -1) is 32 in a random model
+    shape = tuple(32 if int(s) == -1 else int(s) for s in spec.shape)
     n = 1
-    for s in spec.shape:
-        n *= int(s)
-    t = seeded_normal(n, _tensor_seed(seed, spec.name), device).view(spec.shape)
+    for s in shape:
+        n *= s
+    t = seeded_normal(n, _tensor_seed(seed, spec.name), device).view(shape)
     if spec.role == "gain":
         t = 1.0 + gain_sigma * t
     elif spec.role == "constant":
