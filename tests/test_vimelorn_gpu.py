@@ -96,15 +96,17 @@ def _table(rot, base, positions):
                                                (6, 3, 10, 6, 5, 6, 4), (4, 1, 96, 96, 4, 96, 16),
                                                (2, 2, 16, 8, 2, 0, 8), (3, 1, 8, 8, 0, 4, 8)])
 def test_projection_rows_convolved_rotated_normed_and_stored(H, G, a, b, taps, rot, ps, dtype):
-    """Three requests (73, 9 and 1 tokens) cut into portions down to one token, in state slots
+    """Three requests (150, 9 and 1 tokens) cut into portions down to one token, in state slots
     that hold NaN elsewhere; the first token of the long one is loud, so a convolution that
-    loses its kept rows at a portion's start shows at once."""
+    loses its kept rows at a portion's start shows at once. The first step holds all three (the
+    form for prompt portions, whose runs of tokens cross from one request into the next), later
+    ones are long or short enough for either form."""
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(H * 10 + taps)
     C = H * a + G * (a + b)
     eps = 1e-5
-    lengths = [73, 9, 1]
-    cuts = {0: [5, 1, 2, 1, 1, 30, 3, 30], 1: [2, 7], 2: [1]}
+    lengths = [150, 9, 1]
+    cuts = {0: [37, 1, 2, 1, 1, 60, 3, 45], 1: [2, 7], 2: [1]}
     raw = [vt.bf16_values(rng.normal(size=(n, C))) for n in lengths]
     raw[0][0] *= 6.0
     w = rng.normal(0, 0.7, (C, max(taps, 1))).astype(np.float32).astype(np.float64) if taps else None

@@ -1015,16 +1015,37 @@ qkv_conv_rope_norm_cache_kernel(
         const int b = seq_ids[t];
         const int r = t - q_start[b];
         const float* kept = state + (size_t)state_slots[b] * state_stride + conv_offset;
-        for (int i = lane; i < width; i += 32) {
-            const int c = c0 + i;
-            float a = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                const int back = taps - 1 - j;
-                const float u = back <= r ? to_f32(*(row - (size_t)back * qkv_stride + c))
-                                          : kept[(size_t)(taps - 1 - (back - r)) * C + c];
-                a = fmaf(conv_w[(size_t)c * taps + j], u, a);
+        if (r >= taps - 1 && taps == 4 && !((uintptr_t)conv_w & 15)) {
+            // every tap meets a row of this step (all but a portion's first tokens): the four
+            // loads and the weights' one are issued together; the sum keeps the order below
+            for (int i = lane; i < width; i += 32) {
+                const int c = c0 + i;
+                const float4 w4 = *(const float4*)(conv_w + (size_t)c * 4);
+                const T* col = row + c;
+                const float u0 = to_f32(*(col - 3 * (size_t)qkv_stride)), u1 = to_f32(*(col - 2 * (size_t)qkv_stride));
+                const float u2 = to_f32(*(col - (size_t)qkv_stride)), u3 = to_f32(*col);
+                buf[i] = fmaf(w4.w, u3, fmaf(w4.z, u2, fmaf(w4.y, u1, fmaf(w4.x, u0, 0.f))));
             }
-            buf[i] = a;
+        } else if (r >= taps - 1) {
+            for (int i = lane; i < width; i += 32) {
+                const int c = c0 + i;
+                float a = 0.f;
+                for (int j = 0; j < taps; ++j)
+                    a = fmaf(conv_w[(size_t)c * taps + j], to_f32(*(row - (size_t)(taps - 1 - j) * qkv_stride + c)), a);
+                buf[i] = a;
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) {
+                const int c = c0 + i;
+                float a = 0.f;
+                for (int j = 0; j < taps; ++j) {
+                    const int back = taps - 1 - j;
+                    const float u = back <= r ? to_f32(*(row - (size_t)back * qkv_stride + c))
+                                              : kept[(size_t)(taps - 1 - (back - r)) * C + c];
+                    a = fmaf(conv_w[(size_t)c * taps + j], u, a);
+                }
+                buf[i] = a;
+            }
         }
     } else {
         for (int i = lane; i < width; i += 32)
