@@ -42,7 +42,8 @@ def close(got, want, tol, what=""):
 
 # ------------------------------------------------------------------------ kernels alone
 @pytest.mark.parametrize("ydtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,T,d", [(3, 7, 48), (1, 1, 36), (8, 70, 200), (2, 5, 13), (4, 3, 4100)])
+@pytest.mark.parametrize("S,T,d", [(3, 7, 48), (1, 1, 36), (8, 70, 200), (2, 5, 13), (4, 3, 4100), (3, 2, 13000),
+                                   (2, 3, 12289), (5, 9, 1026)])
 def test_streams_read_and_written(S, T, d, ydtype):
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(S * 100 + d)

@@ -642,12 +642,137 @@ stream_read_norm_kernel(const float* __restrict__ x, int S, int T, int d,
         out[t * d + i] = from_f32<TO>((row[i] * r) * gain[i]);
 }
 
+// Four consecutive channels a thread and step (16-byte accesses of the float32 streams): for
+// d % 4 == 0 and rows that start on 16 bytes. Same sums in the same order per channel; the sum of
+// squares adds the four channels of a thread before the block's reduction.
+__device__ __forceinline__ float4 hc_ld4(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 hc_ld4(const bf16* p) {
+    const uint2 r = *(const uint2*)p;
+    const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&r.x);
+    const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&r.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void hc_st4(float* p, float4 v) { *(float4*)p = v; }
+__device__ __forceinline__ void hc_st4(bf16* p, float4 v) {
+    uint2 r;
+    *(__nv_bfloat162*)&r.x = __floats2bfloat162_rn(v.x, v.y);
+    *(__nv_bfloat162*)&r.y = __floats2bfloat162_rn(v.z, v.w);
+    *(uint2*)p = r;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+stream_read_norm_vec_kernel(const float* __restrict__ x, int S, int T, int d,
+                            const float* __restrict__ cin, const float* __restrict__ gain, float eps,
+                            TO* __restrict__ out) {
+    extern __shared__ float4 row4[];           // [d / 4]
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t t = blockIdx.x, plane = (size_t)T * d;
+    float c[HC_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s) c[s] = s < S ? cin[s] : 0.f;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        float4 v[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) v[s] = hc_ld4(x + s * plane + t * d + 4 * i);
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) {
+                u.x = fmaf(c[s], v[s].x, u.x); u.y = fmaf(c[s], v[s].y, u.y);
+                u.z = fmaf(c[s], v[s].z, u.z); u.w = fmaf(c[s], v[s].w, u.w);
+            }
+        row4[i] = u;
+        ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        const float4 u = row4[i], g = *(const float4*)(gain + 4 * i);
+        hc_st4(out + t * d + 4 * i, make_float4((u.x * r) * g.x, (u.y * r) * g.y, (u.z * r) * g.z, (u.w * r) * g.w));
+    }
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+stream_write_vec_kernel(float* __restrict__ x, int S, int T, int d, const TY* __restrict__ y,
+                        const float* __restrict__ mix, const float* __restrict__ cout,
+                        const float* __restrict__ next_in, const float* __restrict__ next_gain, float eps,
+                        TO* __restrict__ next_out, float* __restrict__ sum_out) {
+    extern __shared__ float4 row4[];           // [d / 4] when the next input is made here
+    __shared__ float scratch[33];
+    __shared__ float m[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ni[HC_MAX_STREAMS];
+    pdl_wait();
+    if (threadIdx.x < S * S) m[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        co[threadIdx.x] = cout[threadIdx.x];
+        ni[threadIdx.x] = next_in ? next_in[threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    const size_t t = blockIdx.x, plane = (size_t)T * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        float4 old[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) old[s] = hc_ld4(x + s * plane + t * d + 4 * i);
+        const float4 yv = hc_ld4(y + t * d + 4 * i);
+        float4 u = make_float4(0.f, 0.f, 0.f, 0.f), total = u;
+#pragma unroll
+        for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+            if (to >= S) continue;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) {
+                    const float w = m[s * S + to];
+                    a.x = fmaf(w, old[s].x, a.x); a.y = fmaf(w, old[s].y, a.y);
+                    a.z = fmaf(w, old[s].z, a.z); a.w = fmaf(w, old[s].w, a.w);
+                }
+            a.x = fmaf(co[to], yv.x, a.x); a.y = fmaf(co[to], yv.y, a.y);
+            a.z = fmaf(co[to], yv.z, a.z); a.w = fmaf(co[to], yv.w, a.w);
+            hc_st4(x + to * plane + t * d + 4 * i, a);
+            u.x = fmaf(ni[to], a.x, u.x); u.y = fmaf(ni[to], a.y, u.y);
+            u.z = fmaf(ni[to], a.z, u.z); u.w = fmaf(ni[to], a.w, u.w);
+            total.x += a.x; total.y += a.y; total.z += a.z; total.w += a.w;
+        }
+        if (sum_out) hc_st4(sum_out + t * d + 4 * i, total);
+        if (next_out) {
+            row4[i] = u;
+            ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+        }
+    }
+    if (!next_out) return;
+    ss = block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+        const float4 u = row4[i], g = *(const float4*)(next_gain + 4 * i);
+        hc_st4(next_out + t * d + 4 * i, make_float4((u.x * r) * g.x, (u.y * r) * g.y, (u.z * r) * g.z, (u.w * r) * g.w));
+    }
+}
+
 TGO_API int tgo_stream_read_norm(const float* x, int S, int T, int d, const float* cin,
                                  const float* gain, float eps, void* out, int out_dtype,
                                  cudaStream_t stream) {
     if (T <= 0) return 0;
     if (S <= 0 || S > HC_MAX_STREAMS || d <= 0 || d > 24576) return TGO_E_BAD_ARG;
     const size_t smem = (size_t)d * sizeof(float);
+    const bool vec = d % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)gain & 15) && !((uintptr_t)out & 15);
+    if (vec && out_dtype == TGO_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(stream_read_norm_vec_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(stream_read_norm_vec_kernel<bf16>, dim3(T), dim3(256), smem, stream, x, S, T, d,
+                              cin, gain, eps, (bf16*)out);
+    }
+    if (vec && out_dtype == TGO_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(stream_read_norm_vec_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tgo_launch_pdl(stream_read_norm_vec_kernel<float>, dim3(T), dim3(256), smem, stream, x, S, T, d,
+                              cin, gain, eps, (float*)out);
+    }
     if (out_dtype == TGO_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(stream_read_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -728,10 +853,22 @@ TGO_API int tgo_stream_write(float* x, int S, int T, int d, const void* y, int y
         return tgo_launch_pdl(stream_write_kernel<TY, TO>, dim3(T), dim3(256), smem, stream, x, S, T, d, \
                               (const TY*)y, mix, cout, next_in, next_gain, eps, (TO*)next_out, sum_out); \
     } while (0)
+#define HC_GO4(TY, TO)                                                                             \
+    do {                                                                                           \
+        if (smem > 48 * 1024)                                                                      \
+            cudaFuncSetAttribute(stream_write_vec_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tgo_launch_pdl(stream_write_vec_kernel<TY, TO>, dim3(T), dim3(256), smem, stream, x, S, T, d, \
+                              (const TY*)y, mix, cout, next_in, next_gain, eps, (TO*)next_out, sum_out); \
+    } while (0)
     const bool out_bf = next_out && out_dtype == TGO_BF16;
     if (next_out && out_dtype != TGO_BF16 && out_dtype != TGO_F32) return TGO_E_BAD_ARG;
+    const bool vec = d % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)y & 15) && !((uintptr_t)next_gain & 15) &&
+                     !((uintptr_t)next_out & 15) && !((uintptr_t)sum_out & 15);
+    if (vec && y_dtype == TGO_BF16) { if (out_bf) HC_GO4(bf16, bf16); else HC_GO4(bf16, float); }
+    if (vec && y_dtype == TGO_F32) { if (out_bf) HC_GO4(float, bf16); else HC_GO4(float, float); }
     if (y_dtype == TGO_BF16) { if (out_bf) HC_GO(bf16, bf16); else HC_GO(bf16, float); }
     if (y_dtype == TGO_F32) { if (out_bf) HC_GO(float, bf16); else HC_GO(float, float); }
+#undef HC_GO4
 #undef HC_GO
     return TGO_E_BAD_ARG;
 }
