@@ -94,7 +94,7 @@ def _table(rot, base, positions):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,a,b,taps,rot,ps", [(4, 2, 12, 20, 3, 8, 8), (1, 1, 24, 24, 1, 24, 16),
-                                               (6, 3, 10, 6, 5, 6, 4), (4, 1, 96, 96, 4, 96, 16),
+                                               (6, 3, 10, 6, 5, 6, 4), (4, 1, 80, 80, 4, 80, 16),
                                                (2, 2, 16, 8, 2, 0, 8), (3, 1, 8, 8, 0, 4, 8)])
 def test_projection_rows_convolved_rotated_normed_and_stored(H, G, a, b, taps, rot, ps, dtype):
     """Three requests (150, 9 and 1 tokens) cut into portions down to one token, in state slots
@@ -169,7 +169,7 @@ def test_projection_rows_convolved_rotated_normed_and_stored(H, G, a, b, taps, r
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,a,b,coef,every", [(3, 1, 8, 16, 0.4, 5), (1, 1, 24, 24, 0.2, 1),
-                                              (4, 2, 64, 64, 0.3, 64), (5, 5, 6, 7, 1.5, 3)])
+                                              (4, 2, 48, 48, 0.25, 32), (5, 5, 6, 7, 1.5, 3)])
 def test_whole_row_norm_with_a_query_temperature(H, G, a, b, coef, every, dtype):
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(H + a)
@@ -240,7 +240,7 @@ def _run_attention(fn, q, k, v, H, b, ps, dtype, positions):
 
 
 # (heads, kv heads, key size, value size, page, window, kept first)
-WINDOWS = [(4, 2, 12, 20, 8, 7, 2), (4, 1, 96, 96, 16, 40, 6), (6, 3, 10, 6, 4, 3, 9), (2, 2, 16, 16, 8, 64, 64),
+WINDOWS = [(4, 2, 12, 20, 8, 7, 2), (4, 1, 80, 80, 16, 44, 5), (6, 3, 10, 6, 4, 3, 9), (2, 2, 16, 16, 8, 64, 64),
            (8, 2, 64, 64, 16, 70, 3), (3, 1, 32, 48, 16, 129, 70), (1, 1, 24, 24, 16, 300, 1)]
 
 
@@ -277,7 +277,7 @@ def test_window_with_kept_first_tokens_generic(H, G, a, b, ps, window, keep, dty
     assert np.abs(with_it - without).max() > 1.0
 
 
-TILE_WINDOWS = [(4, 2, 16, 24, 8, 7, 2), (4, 1, 96, 96, 16, 40, 6), (8, 2, 64, 64, 16, 70, 3), (3, 1, 32, 48, 16, 129, 70),
+TILE_WINDOWS = [(4, 2, 16, 24, 8, 7, 2), (4, 1, 80, 80, 16, 44, 5), (8, 2, 64, 64, 16, 70, 3), (3, 1, 32, 48, 16, 129, 70),
                 (2, 2, 128, 128, 16, 64, 64), (20, 1, 16, 16, 16, 33, 5), (5, 5, 40, 40, 8, 200, 130)]
 
 
@@ -311,7 +311,7 @@ def test_window_with_kept_first_tokens_on_the_tensor_cores(H, G, a, b, ps, windo
                   f"single tokens in {splits} shares, loud {loud}")
 
 
-BIASES = [(3, 1, 8, 16, 8, 10, 30), (1, 1, 24, 24, 16, 2, 3), (4, 2, 64, 32, 16, 32, 120), (5, 5, 6, 7, 4, 7, 17),
+BIASES = [(3, 1, 8, 16, 8, 10, 30), (1, 1, 24, 24, 16, 2, 3), (4, 2, 64, 32, 16, 30, 110), (5, 5, 6, 7, 4, 7, 17),
           (20, 1, 16, 16, 16, 32, 200)]
 
 

@@ -10,7 +10,7 @@
       1 of experts without identity or shared expert, a temperature every position, a table
       of two rows, one head.
   V3: sizes the tensor-core kernels take (head sizes multiples of 16, expert widths multiples
-      of 8), a window of 40 with 6 kept on pages of 16, more query heads per kv head than a
+      of 8), a window of 44 with 5 kept on pages of 16, more query heads per kv head than a
       decode tile of 16 rows in the causal layer, many experts.
   V4: sizes that no kernel's fast form takes (a width, head sizes, expert widths and a
       vocabulary that are not multiples of 8), more kept tokens than a page holds, a window
@@ -71,11 +71,11 @@ V3 = {
     "architecture": "Vimelorn", "vocab": 96, "width": 64, "norm": {"eps": 1e-6}, "streams": 2,
     "embedding": {"scale": 8.0},
     "layers": [
-        {"type": "attention", "mixer": _win(4, 1, 32, 48, 4, {"dims": 16, "base": 10000.0}, 40, 6, 0.18),
-         "mlp": _moe(12, 2, 3, 32, 40)},
-        {"type": "attention_2", "mixer": _causal(20, 1, 16, 16, 0.3, 64, 120, 0.25),
+        {"type": "attention", "mixer": _win(4, 1, 32, 48, 4, {"dims": 16, "base": 10000.0}, 44, 5, 0.18),
+         "mlp": _moe(12, 3, 4, 32, 40)},
+        {"type": "attention_2", "mixer": _causal(20, 1, 16, 16, 0.25, 32, 150, 0.25),
          "mlp": {"kind": "dense", "ff": 96}},
-        {"type": "attention", "mixer": _win(8, 2, 64, 64, 4, {"dims": 64, "base": 250000.0}, 70, 3, 0.125),
+        {"type": "attention", "mixer": _win(8, 2, 64, 64, 3, {"dims": 64, "base": 100000.0}, 70, 3, 0.125),
          "mlp": None},
         {"type": "attention_2", "mixer": _causal(4, 2, 64, 32, 0.3, 16, 200, 0.125),
          "mlp": _moe(4, 0, 2, 64, 0)},
@@ -102,7 +102,7 @@ V5 = {
 }
 
 CONFIGS = {"V1": (V1, 8), "V2": (V2, 16), "V3": (V3, 16), "V4": (V4, 4), "V5": (V5, 8)}   # config, page
-REL_ROWS = {"V1": 10, "V2": 2, "V3": 32, "V4": 7, "V5": 6}     # rows of the distance tables
+REL_ROWS = {"V1": 10, "V2": 2, "V3": 24, "V4": 7, "V5": 6}     # rows of the distance tables
 
 
 def bf16_values(x: np.ndarray) -> np.ndarray:
