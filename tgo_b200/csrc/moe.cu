@@ -461,6 +461,10 @@ TGO_API int tgo_moe_route(const void* x, long long x_stride, int dtype, const fl
     int rc = E_real ? (int)cudaMemsetAsync(counts, 0, sizeof(int) * E_real, stream) : 0;
     if (rc) return rc;
     const size_t smem = (size_t)MOE_RT * (2 * E + 1) * sizeof(float);
+    if (smem > 48 * 1024) {                              // more than about 1500 router outputs
+        cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     if (dtype == TGO_BF16)
         moe_route_kernel<bf16><<<(T + MOE_RT - 1) / MOE_RT, 128, smem, stream>>>((const bf16*)x, x_stride, wr, br, T, d, E,
                                                                   top, ids, wts, counts, score_mode, correction, E_real, gate_out);
