@@ -99,9 +99,9 @@ def _table(rot, base, positions):
 def test_projection_rows_convolved_rotated_normed_and_stored(H, G, a, b, taps, rot, ps, dtype):
     """Three requests (150, 9 and 1 tokens) cut into portions down to one token, in state slots
     that hold NaN elsewhere; the first token of the long one is loud, so a convolution that
-    loses its kept rows at a portion's start shows at once. The first step holds all three (the
-    form for prompt portions, whose runs of tokens cross from one request into the next), later
-    ones are long or short enough for either form."""
+    loses its kept rows at a portion's start shows at once. The first step holds all three, so
+    that tokens whose taps all meet rows of the step lie beside tokens at the start of another
+    request's portion, whose taps meet kept rows or nothing."""
     from tgo_b200.kernels import ops
     rng = np.random.default_rng(H * 10 + taps)
     C = H * a + G * (a + b)
